@@ -1,0 +1,97 @@
+// extern "C" surface of the engine; see include/cuhnsw_b200.h for the contract.
+#include <exception>
+#include <new>
+
+#include "../../include/cuhnsw_b200.h"
+#include "engine.h"
+
+struct cuhnsw_handle {
+  hnsw::Engine engine;
+  std::string fatal;
+};
+
+namespace {
+template <class F>
+int guarded(cuhnsw_handle* h, F f) {
+  if (!h) return CUHNSW_INVALID_ARGUMENT;
+  try {
+    return f(h->engine);
+  } catch (const std::bad_alloc&) {
+    h->fatal = "out of host memory";
+  } catch (const std::exception& e) {
+    h->fatal = e.what();
+  } catch (...) {
+    h->fatal = "unknown failure";
+  }
+  return CUHNSW_INVALID_ARGUMENT;
+}
+}  // namespace
+
+extern "C" {
+
+cuhnsw_handle* cuhnsw_create(void) {
+  try {
+    return new cuhnsw_handle();
+  } catch (...) {
+    return nullptr;
+  }
+}
+void cuhnsw_destroy(cuhnsw_handle* h) { delete h; }
+const char* cuhnsw_last_error(const cuhnsw_handle* h) {
+  if (!h) return "null handle";
+  return h->fatal.empty() ? h->engine.last_error() : h->fatal.c_str();
+}
+int cuhnsw_init(cuhnsw_handle* h, const char* opt_path) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.Init(opt_path); });
+}
+int cuhnsw_set_data(cuhnsw_handle* h, const float* data, int64_t num_data, int32_t num_dims) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.SetData(data, num_data, num_dims); });
+}
+int cuhnsw_set_random_levels(cuhnsw_handle* h, const int32_t* levels) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.SetRandomLevels(levels); });
+}
+int cuhnsw_build_graph(cuhnsw_handle* h) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.BuildGraph(); });
+}
+int cuhnsw_save_index(cuhnsw_handle* h, const char* fpath) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.SaveIndex(fpath); });
+}
+int cuhnsw_load_index(cuhnsw_handle* h, const char* fpath) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.LoadIndex(fpath); });
+}
+int cuhnsw_search_knn(cuhnsw_handle* h, const float* qdata, int64_t num_queries, int32_t topk, int32_t ef_search,
+                      int32_t* nns, float* distances, int32_t* found_cnt) {
+  return guarded(h, [&](hnsw::Engine& e) {
+    return e.SearchGraph(qdata, num_queries, topk, ef_search, nns, distances, found_cnt);
+  });
+}
+int cuhnsw_search_knn_device(cuhnsw_handle* h, const float* d_qdata, int64_t num_queries, int32_t topk,
+                             int32_t ef_search, int32_t* d_nns, float* d_distances, int32_t* d_found_cnt) {
+  return guarded(h, [&](hnsw::Engine& e) {
+    return e.SearchGraphDevice(d_qdata, num_queries, topk, ef_search, d_nns, d_distances, d_found_cnt);
+  });
+}
+int cuhnsw_batch_distance(cuhnsw_handle* h, const int32_t* src, const int32_t* dst, int64_t num_pairs, float* out) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.BatchDistance(src, dst, num_pairs, out); });
+}
+int cuhnsw_set_stream(cuhnsw_handle* h, void* cuda_stream) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.SetStream(cuda_stream); });
+}
+int cuhnsw_synchronize(cuhnsw_handle* h) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.Synchronize(); });
+}
+int cuhnsw_enable_stats(cuhnsw_handle* h, int32_t on) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.EnableStats(on); });
+}
+int cuhnsw_get_stats(cuhnsw_handle* h, uint64_t* out4) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.GetStats(reinterpret_cast<unsigned long long*>(out4)); });
+}
+int cuhnsw_describe(cuhnsw_handle* h, int64_t* out8) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.Describe(reinterpret_cast<long long*>(out8)); });
+}
+int cuhnsw_get_graph(cuhnsw_handle* h, int32_t* levels, int32_t* rows0, int32_t* rows_upper) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.GetGraph(levels, rows0, rows_upper); });
+}
+double cuhnsw_last_build_seconds(const cuhnsw_handle* h) { return h ? h->engine.last_build_seconds() : 0.0; }
+
+}  // extern "C"

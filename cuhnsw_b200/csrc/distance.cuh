@@ -1,0 +1,202 @@
+// Canonical fp32 distance for warps (replaces cpp/include/cuda_dist_kernels.cuh:13-140
+// of the reference: block-strided scalar loads + shared-memory broadcast).
+//
+// Summation order (identical in the CPU oracle, so distances are bit-equal):
+//   W = 32 accumulators when d <= 128, else 128.  Element i is fused-multiply-
+//   added into accumulator (i mod W) in increasing i.  A "team" of T = W/4
+//   lanes owns one row; lane t owns accumulators 4t..4t+3, i.e. the float4
+//   chunks t, t+T, t+2T, ... of the row, so every load is a 16-byte vector and
+//   a team reads T*16 contiguous bytes per instruction.  The four accumulators
+//   of a lane fold as (a0+a1)+(a2+a3); lanes fold by an xor butterfly with
+//   offsets T/2..1.  DOT returns -sum, L2 the squared distance
+//   (cuda_dist_kernels.cuh:112-124).
+//
+// Rows are stored padded with zeros to a multiple of 8 floats (32-byte sectors).
+#pragma once
+#include "common.cuh"
+
+namespace hnsw {
+
+struct VecTable {
+  const float4* vec;  // n rows
+  int stride4;        // row stride in float4 units
+  int nchunk;         // ceil(d / 4): chunks that hold data
+  int d;
+  int dist_type;
+};
+
+__device__ __forceinline__ float4 ldg4(const float4* p) { return __ldg(p); }
+
+__device__ __forceinline__ void fma4(float4& acc, const float4& a, const float4& b, int dist_type) {
+  if (dist_type == DIST_DOT) {
+    acc.x = fmaf(a.x, b.x, acc.x);
+    acc.y = fmaf(a.y, b.y, acc.y);
+    acc.z = fmaf(a.z, b.z, acc.z);
+    acc.w = fmaf(a.w, b.w, acc.w);
+  } else {
+    float dx = a.x - b.x, dy = a.y - b.y, dz = a.z - b.z, dw = a.w - b.w;
+    acc.x = fmaf(dx, dx, acc.x);
+    acc.y = fmaf(dy, dy, acc.y);
+    acc.z = fmaf(dz, dz, acc.z);
+    acc.w = fmaf(dw, dw, acc.w);
+  }
+}
+
+__device__ __forceinline__ float fold4(const float4& a) { return (a.x + a.y) + (a.z + a.w); }
+
+// ---------------------------------------------------------------------------
+// d <= 128: teams of 8 lanes, four rows per warp pass, query chunks in registers.
+// C = ceil(d / 32) chunks per lane.
+// ---------------------------------------------------------------------------
+template <int C>
+struct DistSmall {
+  static constexpr int kTeam = 8;
+  static constexpr int kRowsPerPass = 4;
+  static constexpr int kBatch = (C <= 2) ? 6 : 4;  // passes whose loads are issued together
+  __host__ __device__ static constexpr size_t smem_bytes(int) { return 0; }
+
+  VecTable t;
+  float4 q[C];
+
+  __device__ __forceinline__ void init(const VecTable& tab, void*) { t = tab; }
+
+  // query from an unpadded row of d floats in global memory
+  __device__ __forceinline__ void load_query(const float* qp) {
+    const int tl = lane_id() & 7;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      int e = 4 * (tl + 8 * c);
+      q[c].x = (e + 0 < t.d) ? __ldg(qp + e + 0) : 0.0f;
+      q[c].y = (e + 1 < t.d) ? __ldg(qp + e + 1) : 0.0f;
+      q[c].z = (e + 2 < t.d) ? __ldg(qp + e + 2) : 0.0f;
+      q[c].w = (e + 3 < t.d) ? __ldg(qp + e + 3) : 0.0f;
+    }
+  }
+  // query = stored (padded) row `id`
+  __device__ __forceinline__ void load_query_row(int id) {
+    const int tl = lane_id() & 7;
+    const float4* row = t.vec + (size_t)id * t.stride4;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      int ch = tl + 8 * c;
+      q[c] = (ch < t.nchunk) ? ldg4(row + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+
+  // Lane r (r < n <= 32) holds a row id; returns the distance to it in lane r.
+  __device__ __forceinline__ float eval(int id, int n) {
+    const int lane = lane_id();
+    const int team = lane >> 3, tl = lane & 7;
+    const int npass = (n + 3) >> 2;
+    float result = 0.0f;
+    for (int p0 = 0; p0 < npass; p0 += kBatch) {
+      float4 v[kBatch][C];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        int r = (p0 + u) * 4 + team;
+        int rid = __shfl_sync(FULL, id, r & 31);
+        bool ok = (p0 + u < npass) && (r < n);
+        const float4* row = t.vec + (size_t)(ok ? rid : 0) * t.stride4;
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          int ch = tl + 8 * c;
+          v[u][c] = (ok && ch < t.nchunk) ? ldg4(row + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        if (p0 + u < npass) {  // warp-uniform
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int c = 0; c < C; ++c) fma4(acc, q[c], v[u][c], t.dist_type);
+          float s = fold4(acc);
+          s += __shfl_xor_sync(FULL, s, 4);
+          s += __shfl_xor_sync(FULL, s, 2);
+          s += __shfl_xor_sync(FULL, s, 1);
+          if (t.dist_type == DIST_DOT) s = -s;
+          float mine = __shfl_sync(FULL, s, (lane & 3) << 3);
+          if ((lane >> 2) == p0 + u) result = mine;
+        }
+      }
+    }
+    return result;
+  }
+};
+
+// ---------------------------------------------------------------------------
+// d > 128: the whole warp owns one row (T = 32), query chunks in shared memory.
+// ---------------------------------------------------------------------------
+struct DistLarge {
+  static constexpr int kRows = 4;    // rows whose loads are in flight together
+  static constexpr int kChunks = 4;  // chunk columns per row per step
+  __host__ __device__ static constexpr size_t smem_bytes(int d) { return (size_t)((d + 127) / 128) * 128 * sizeof(float); }
+
+  VecTable t;
+  float4* sq;  // per-warp, (C * 32) float4, zero padded
+  int C;
+
+  __device__ __forceinline__ void init(const VecTable& tab, void* smem) {
+    t = tab;
+    sq = reinterpret_cast<float4*>(smem);
+    C = (tab.d + 127) / 128;
+  }
+  __device__ __forceinline__ void load_query(const float* qp) {
+    float* s = reinterpret_cast<float*>(sq);
+    for (int e = lane_id(); e < C * 128; e += 32) s[e] = (e < t.d) ? __ldg(qp + e) : 0.0f;
+    __syncwarp();
+  }
+  __device__ __forceinline__ void load_query_row(int id) {
+    const float4* row = t.vec + (size_t)id * t.stride4;
+    for (int ch = lane_id(); ch < C * 32; ch += 32)
+      sq[ch] = (ch < t.nchunk) ? ldg4(row + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+    __syncwarp();
+  }
+  __device__ __forceinline__ float eval(int id, int n) {
+    const int lane = lane_id();
+    float result = 0.0f;
+    for (int r0 = 0; r0 < n; r0 += kRows) {
+      float4 acc[kRows];
+      int rid[kRows];
+#pragma unroll
+      for (int u = 0; u < kRows; ++u) {
+        acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        rid[u] = __shfl_sync(FULL, id, (r0 + u) & 31);
+        if (r0 + u >= n) rid[u] = -1;
+      }
+      for (int c0 = 0; c0 < C; c0 += kChunks) {
+        float4 v[kRows][kChunks];
+#pragma unroll
+        for (int u = 0; u < kRows; ++u) {
+          const float4* row = t.vec + (size_t)(rid[u] >= 0 ? rid[u] : 0) * t.stride4;
+#pragma unroll
+          for (int cc = 0; cc < kChunks; ++cc) {
+            int ch = lane + 32 * (c0 + cc);
+            v[u][cc] = (rid[u] >= 0 && ch < t.nchunk) ? ldg4(row + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+#pragma unroll
+        for (int cc = 0; cc < kChunks; ++cc) {
+          if (c0 + cc < C) {
+            float4 qq = sq[lane + 32 * (c0 + cc)];
+#pragma unroll
+            for (int u = 0; u < kRows; ++u) fma4(acc[u], qq, v[u][cc], t.dist_type);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kRows; ++u) {
+        float s = fold4(acc[u]);
+        s += __shfl_xor_sync(FULL, s, 16);
+        s += __shfl_xor_sync(FULL, s, 8);
+        s += __shfl_xor_sync(FULL, s, 4);
+        s += __shfl_xor_sync(FULL, s, 2);
+        s += __shfl_xor_sync(FULL, s, 1);
+        if (t.dist_type == DIST_DOT) s = -s;
+        if (lane == r0 + u) result = s;
+      }
+    }
+    return result;
+  }
+};
+
+}  // namespace hnsw

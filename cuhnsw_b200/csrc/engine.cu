@@ -1,0 +1,714 @@
+#include "engine.h"
+
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <sstream>
+
+#include "json_min.h"
+
+namespace hnsw {
+
+namespace {
+constexpr int kMaxLinksHost = 64;
+constexpr int kMaxEf = 8192;
+
+int round_up(int x, int m) { return (x + m - 1) / m * m; }
+int next_pow2(long long x) {
+  int p = 1;
+  while (p < x) p <<= 1;
+  return p;
+}
+
+#pragma pack(push, 1)
+// Header of an hnswlib index file as the reference writes it (cpp/src/cuhnsw_base.cu:182-194).
+struct FileHeader {
+  uint64_t offset_level0;
+  uint64_t max_elements;
+  uint64_t cur_element_count;
+  uint64_t size_data_per_element;
+  uint64_t label_offset;
+  uint64_t offset_data;
+  int32_t maxlevel;
+  uint32_t enterpoint_node;
+  uint64_t max_m;
+  uint64_t max_m0;
+  uint64_t m;
+  double mult;
+  uint64_t ef_construction;
+};
+#pragma pack(pop)
+static_assert(sizeof(FileHeader) == 96, "hnswlib header is 96 bytes");
+}  // namespace
+
+Engine::Engine() {}
+Engine::~Engine() {}
+
+int Engine::Fail(int code, const std::string& msg) {
+  err_ = msg;
+  if (opt_.c_log_level >= 1) std::fprintf(stderr, "[cuhnsw_b200] error: %s\n", msg.c_str());
+  return code;
+}
+
+int Engine::FailCuda(cudaError_t e, const char* what) {
+  std::ostringstream os;
+  os << "CUDA error in " << what << ": " << cudaGetErrorString(e);
+  return Fail(kCudaError, os.str());
+}
+
+void Engine::Log(int level, const char* fmt, ...) const {
+  if (opt_.c_log_level < level) return;
+  va_list ap;
+  va_start(ap, fmt);
+  std::fprintf(stderr, "[cuhnsw_b200] ");
+  std::vfprintf(stderr, fmt, ap);
+  std::fprintf(stderr, "\n");
+  va_end(ap);
+}
+
+#define CU(call)                                         \
+  do {                                                   \
+    cudaError_t e__ = (call);                            \
+    if (e__ != cudaSuccess) return FailCuda(e__, #call); \
+  } while (0)
+
+int Engine::EnsureDevice() {
+  if (device_ >= 0) {
+    CU(cudaSetDevice(device_));
+    return kOk;
+  }
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    return Fail(kCudaError, "no CUDA device: this library has no CPU path");
+  int dev = 0;
+  if (opt_.device_id >= 0) {
+    dev = opt_.device_id;
+    CU(cudaSetDevice(dev));
+  } else {
+    CU(cudaGetDevice(&dev));
+  }
+  cudaDeviceProp prop;
+  CU(cudaGetDeviceProperties(&prop, dev));
+  device_ = dev;
+  sm_count_ = prop.multiProcessorCount;
+  smem_optin_ = prop.sharedMemPerBlockOptin;
+  CU(counters_.alloc(8));
+  CU(cudaMemset(counters_.get(), 0, 8 * sizeof(unsigned long long)));
+  Log(3, "device %d: %s, sm_%d%d, %d SMs, %zu B shared memory per block", dev, prop.name, prop.major, prop.minor,
+      sm_count_, smem_optin_);
+  return kOk;
+}
+
+int Engine::Init(const char* opt_path) {
+  if (!opt_path) return Fail(kInvalidArgument, "null option path");
+  std::ifstream in(opt_path);
+  if (!in.is_open()) return Fail(kIoError, std::string("cannot open option file ") + opt_path);
+  std::string text((std::istreambuf_iterator<char>(in)), std::istreambuf_iterator<char>());
+  FlatJson js;
+  if (!js.parse(text)) return Fail(kParseError, std::string("invalid option file ") + opt_path);
+  Options o;
+  o.seed = (int)js.number("seed", o.seed);
+  o.c_log_level = (int)js.number("c_log_level", o.c_log_level);
+  o.max_m = (int)js.number("max_m", o.max_m);
+  o.max_m0 = (int)js.number("max_m0", o.max_m0);
+  o.ef_construction = (int)js.number("ef_construction", o.ef_construction);
+  o.level_mult = js.number("level_mult", o.level_mult);
+  o.save_remains = js.boolean("save_remains", o.save_remains);
+  o.hyper_threads = js.number("hyper_threads", o.hyper_threads);
+  o.block_dim = (int)js.number("block_dim", o.block_dim);
+  o.dist_type = js.string("dist_type", o.dist_type);
+  o.visited_table_size = (int)js.number("visited_table_size", o.visited_table_size);
+  o.visited_list_size = (int)js.number("visited_list_size", o.visited_list_size);
+  o.nrz = js.boolean("nrz", o.nrz);
+  o.reverse_cand = js.boolean("reverse_cand", o.reverse_cand);
+  // the reference's schema spells it heuristic_coef, its README heuristic_coff
+  o.heuristic_coef = js.number("heuristic_coef", js.number("heuristic_coff", o.heuristic_coef));
+  o.batch_max = (long long)js.number("batch_max", (double)o.batch_max);
+  o.ramp_div = (long long)js.number("ramp_div", (double)o.ramp_div);
+  o.device_id = (int)js.number("device_id", o.device_id);
+  opt_.c_log_level = o.c_log_level;
+  if (o.dist_type == "dot") dist_type_ = 0;
+  else if (o.dist_type == "l2") dist_type_ = 1;
+  else return Fail(kInvalidOption, "invalid dist type " + o.dist_type);
+  if (o.max_m < 1 || o.max_m0 < 1 || o.max_m > o.max_m0 || o.max_m0 > kMaxLinksHost)
+    return Fail(kInvalidOption, "need 1 <= max_m <= max_m0 <= 64");
+  if (o.ef_construction < 1 || o.ef_construction > kMaxEf)
+    return Fail(kInvalidOption, "need 1 <= ef_construction <= 8192");
+  if (o.heuristic_coef < 0.0 || o.heuristic_coef > 1.0)
+    return Fail(kInvalidOption, "need 0 <= heuristic_coef <= 1");
+  if (o.block_dim < 32 || o.block_dim > 1024 || o.block_dim % 32) return Fail(kInvalidOption, "invalid block_dim");
+  if (o.reverse_cand)
+    return Fail(kUnsupported, "reverse_cand=true (expand the farthest candidate first) is not implemented");
+  if (o.ramp_div < 1) o.ramp_div = 1;
+  opt_ = o;
+  inited_ = true;
+  Log(3, "max_m: %d, max_m0: %d, save_remains: %d, ef_construction: %d, level_mult: %f, dist_type: %s", o.max_m,
+      o.max_m0, (int)o.save_remains, o.ef_construction, o.level_mult, o.dist_type.c_str());
+  return kOk;
+}
+
+int Engine::SetStream(void* stream) {
+  stream_ = reinterpret_cast<cudaStream_t>(stream);
+  return kOk;
+}
+
+int Engine::Synchronize() {
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  CU(cudaStreamSynchronize(stream_));
+  return kOk;
+}
+
+int Engine::SetData(const float* data, long long num_data, int num_dims) {
+  if (!inited_) return Fail(kBadState, "init() must be called first");
+  if (!data && num_data > 0) return Fail(kInvalidArgument, "null data");
+  if (num_data < 0 || num_dims < 1) return Fail(kInvalidArgument, "data must be a 2-d array with at least one column");
+  if (num_data >= (1ll << 31) - 1) return Fail(kUnsupported, "at most 2^31 - 2 rows per index");
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  n_ = num_data;
+  d_ = num_dims;
+  vstride_ = round_up(num_dims, 8);
+  has_levels_ = has_graph_ = labelled_ = false;
+  labels_h_.clear();
+  labels_d_.release();
+  CU(vec_.alloc((size_t)n_ * vstride_));
+  // stage through a bounded device buffer and pad rows on the device
+  const long long rows_per_chunk = std::max<long long>(1, (64ll << 20) / num_dims);
+  DevBuf<float> raw;
+  CU(raw.alloc((size_t)std::min(rows_per_chunk, std::max<long long>(n_, 1)) * num_dims));
+  for (long long s = 0; s < n_; s += rows_per_chunk) {
+    long long r = std::min(rows_per_chunk, n_ - s);
+    CU(cudaMemcpyAsync(raw.get(), data + (size_t)s * num_dims, (size_t)r * num_dims * sizeof(float),
+                       cudaMemcpyHostToDevice, stream_));
+    CU(launch_pad_rows(raw.get(), vec_.get() + (size_t)s * vstride_, r, num_dims, vstride_, stream_));
+    CU(cudaStreamSynchronize(stream_));
+  }
+  has_data_ = true;
+  Log(3, "copied data (%lld x %d), row stride %d floats", n_, d_, vstride_);
+  return kOk;
+}
+
+int Engine::AllocGraph() {
+  stride0_ = round_up(opt_.max_m0, 8);
+  strideU_ = round_up(opt_.max_m, 8);
+  upper_base_h_.assign((size_t)n_, 0);
+  long long acc = 0;
+  for (long long i = 0; i < n_; ++i) {
+    upper_base_h_[i] = (int)acc;
+    acc += levels_h_[i];
+    if (acc > (1ll << 30)) return Fail(kUnsupported, "too many upper-layer rows");
+  }
+  total_upper_ = acc;
+  CU(rows0_.alloc((size_t)n_ * stride0_));
+  CU(rowsU_.alloc((size_t)std::max<long long>(total_upper_, 1) * strideU_));
+  CU(levels_d_.alloc((size_t)std::max<long long>(n_, 1)));
+  CU(upper_base_d_.alloc((size_t)std::max<long long>(n_, 1)));
+  CU(launch_fill_i32(rows0_.get(), n_ * stride0_, -1, stream_));
+  CU(launch_fill_i32(rowsU_.get(), std::max<long long>(total_upper_, 1) * strideU_, -1, stream_));
+  if (n_ > 0) {
+    CU(cudaMemcpyAsync(levels_d_.get(), levels_h_.data(), (size_t)n_ * sizeof(int), cudaMemcpyHostToDevice, stream_));
+    CU(cudaMemcpyAsync(upper_base_d_.get(), upper_base_h_.data(), (size_t)n_ * sizeof(int), cudaMemcpyHostToDevice,
+                       stream_));
+  }
+  CU(cudaStreamSynchronize(stream_));
+  return kOk;
+}
+
+// Level membership and enter point exactly as cpp/src/cuhnsw_base.cu:130-156:
+// node i belongs to levels 0..levels[i]; the enter point is the first node that
+// reaches the maximum level.
+int Engine::SetRandomLevels(const int* levels) {
+  if (!has_data_) return Fail(kBadState, "set_data() must be called first");
+  if (!levels && n_ > 0) return Fail(kInvalidArgument, "null levels");
+  levels_h_.assign((size_t)n_, 0);
+  max_level_ = 0;
+  enter_point_ = 0;
+  for (long long i = 0; i < n_; ++i) {
+    if (levels[i] < 0 || levels[i] > 64) return Fail(kInvalidArgument, "levels must lie in 0..64");
+    levels_h_[i] = levels[i];
+    if (levels[i] > max_level_) {
+      max_level_ = levels[i];
+      enter_point_ = (int)i;
+    }
+  }
+  int rc = AllocGraph();
+  if (rc) return rc;
+  has_levels_ = true;
+  has_graph_ = false;
+  Log(3, "max level: %d, enter point: %d", max_level_, enter_point_);
+  return kOk;
+}
+
+GraphView Engine::View() const {
+  GraphView g;
+  g.vec = vec_.get();
+  g.vstride = vstride_;
+  g.d = d_;
+  g.dist_type = dist_type_;
+  g.n = n_;
+  g.rows0 = rows0_.get();
+  g.stride0 = stride0_;
+  g.rowsU = rowsU_.get();
+  g.strideU = strideU_;
+  g.upper_base = upper_base_d_.get();
+  g.max_level = max_level_;
+  g.enter_point = enter_point_;
+  return g;
+}
+
+int Engine::ResolveVsize(int cap, int* vsize) const {
+  int v;
+  if (opt_.visited_table_size > 0) v = std::min(32768, std::max(64, next_pow2(opt_.visited_table_size)));
+  else v = std::min(4096, std::max(512, next_pow2(16ll * cap)));
+  while (v > 64 && search_smem_per_cta(d_, cap, v) + 4096 > smem_optin_) v >>= 1;
+  if (search_smem_per_cta(d_, cap, v) + 4096 > smem_optin_) return kUnsupported;
+  *vsize = v;
+  return kOk;
+}
+
+int Engine::BuildGraph() {
+  if (!has_levels_) return Fail(kBadState, "set_random_levels() must be called before build_graph()");
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  auto t0 = std::chrono::steady_clock::now();
+  if (n_ == 0) {
+    has_graph_ = true;
+    return kOk;
+  }
+  // insertion batch: the reference keeps hyper_threads * cores / block_dim blocks in flight,
+  // cores = SMs * 128 for this architecture (cpp/src/cuhnsw_base.cu:53-57,111)
+  long long bmax = opt_.batch_max > 0 ? opt_.batch_max
+                                      : (long long)(opt_.hyper_threads * (double)(sm_count_ * 128 / opt_.block_dim));
+  bmax = std::max<long long>(1, std::min(bmax, n_));
+  const int smax = std::max(stride0_, strideU_);
+  int vsize = 0;
+  if (ResolveVsize(std::max(opt_.ef_construction, kMaxLinksHost + 8), &vsize) != kOk)
+    return Fail(kUnsupported, "ef_construction does not fit in shared memory");
+  DevBuf<float> dist0, distU, st_dist;
+  DevBuf<unsigned char> went;
+  DevBuf<int> st_ids, nodes_d;
+  DevBuf<unsigned> pkeys, pkeys_sorted;
+  DevBuf<unsigned long long> pvals, pvals_sorted;
+  DevBuf<unsigned char> sort_tmp;
+  CU(dist0.alloc((size_t)n_ * stride0_));
+  CU(distU.alloc((size_t)std::max<long long>(total_upper_, 1) * strideU_));
+  CU(went.alloc((size_t)n_));
+  CU(st_ids.alloc((size_t)bmax * smax));
+  CU(st_dist.alloc((size_t)bmax * smax));
+  CU(pkeys.alloc((size_t)bmax * smax));
+  CU(pkeys_sorted.alloc((size_t)bmax * smax));
+  CU(pvals.alloc((size_t)bmax * smax));
+  CU(pvals_sorted.alloc((size_t)bmax * smax));
+  size_t tmp_bytes = build_sort_tmp_bytes(bmax * smax);
+  CU(sort_tmp.alloc(tmp_bytes + 256));
+  // rows start empty on every level
+  CU(launch_fill_i32(rows0_.get(), n_ * stride0_, -1, stream_));
+  CU(launch_fill_i32(rowsU_.get(), std::max<long long>(total_upper_, 1) * strideU_, -1, stream_));
+
+  std::vector<std::vector<int>> level_nodes((size_t)max_level_ + 1);
+  for (long long i = 0; i < n_; ++i)
+    for (int l = 1; l <= levels_h_[i]; ++l) level_nodes[l].push_back((int)i);
+  size_t max_upper_nodes = max_level_ >= 1 ? level_nodes[1].size() : 0;
+  CU(nodes_d.alloc(std::max<size_t>(max_upper_nodes, 1)));
+
+  BuildScratch S;
+  S.st_ids = st_ids.get();
+  S.st_dist = st_dist.get();
+  S.pkeys = pkeys.get();
+  S.pkeys_sorted = pkeys_sorted.get();
+  S.pvals = pvals.get();
+  S.pvals_sorted = pvals_sorted.get();
+  S.sort_tmp = sort_tmp.get();
+  S.sort_tmp_bytes = tmp_bytes;
+  S.ticket = counters_.get() + 1;
+  S.stats = stats_on_ ? counters_.get() + 4 : nullptr;
+
+  long long batches = 0;
+  for (int l = max_level_; l >= 0; --l) {
+    const long long nl = l == 0 ? n_ : (long long)level_nodes[l].size();
+    const long long upper_cnt = l < max_level_ ? (long long)level_nodes[l + 1].size() : 0;
+    if (l > 0) {
+      // the previous level's launches still read nodes_d
+      CU(cudaStreamSynchronize(stream_));
+      CU(cudaMemcpyAsync(nodes_d.get(), level_nodes[l].data(), (size_t)nl * sizeof(int), cudaMemcpyHostToDevice,
+                         stream_));
+    } else {
+      CU(cudaStreamSynchronize(stream_));
+    }
+    BuildLevel L;
+    L.g = View();
+    L.level = l;
+    L.rows = l == 0 ? rows0_.get() : rowsU_.get();
+    L.dists = l == 0 ? dist0.get() : distU.get();
+    L.distU = distU.get();
+    L.stride = l == 0 ? stride0_ : strideU_;
+    L.max_m = l == 0 ? opt_.max_m0 : opt_.max_m;
+    L.levels = levels_d_.get();
+    L.nodes = l == 0 ? nullptr : nodes_d.get();
+    L.n_level = nl;
+    L.went = went.get();
+    L.ef_construction = opt_.ef_construction;
+    L.heuristic_coef = (float)opt_.heuristic_coef;
+    L.save_remains = opt_.save_remains ? 1 : 0;
+    L.vsize = vsize;
+    CU(launch_init_level(L, counters_.get() + 3, sm_count_, stream_));
+    long long p = 0;
+    while (p < nl) {
+      long long b = (upper_cnt + p) / opt_.ramp_div;
+      b = std::max<long long>(1, std::min(b, bmax));
+      b = std::min(b, nl - p);
+      CU(launch_build_batch(L, S, p, (int)b, sm_count_, stream_));
+      p += b;
+      ++batches;
+    }
+    Log(3, "level %d: %lld nodes queued", l, nl);
+  }
+  CU(cudaStreamSynchronize(stream_));
+  has_graph_ = true;
+  last_build_seconds_ = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+  Log(2, "built %lld nodes, %d levels, %lld batches (max %lld) in %.3f s", n_, max_level_ + 1, batches, bmax,
+      last_build_seconds_);
+  return kOk;
+}
+
+int Engine::SearchGraphDevice(const float* d_q, long long nq, int topk, int ef, int* d_nns, float* d_dist,
+                              int* d_found) {
+  if (!has_graph_) return Fail(kBadState, "no graph: call build_graph() or load_index() first");
+  if (nq < 0 || topk < 1) return Fail(kInvalidArgument, "need num_queries >= 0 and topk >= 1");
+  if (nq == 0) return kOk;
+  if (!d_q || !d_nns || !d_dist || !d_found) return Fail(kInvalidArgument, "null buffer");
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  ef = std::max(ef, topk);  // cuhnsw/pyhnsw.py:80
+  if (ef > kMaxEf) return Fail(kUnsupported, "ef_search above 8192 is not supported");
+  if (n_ == 0) {
+    CU(cudaMemsetAsync(d_found, 0, (size_t)nq * sizeof(int), stream_));
+    CU(launch_fill_i32(d_nns, nq * topk, -1, stream_));
+    CU(cudaMemsetAsync(d_dist, 0x7f, (size_t)nq * topk * sizeof(float), stream_));
+    return kOk;
+  }
+  int vsize = 0;
+  if (ResolveVsize(ef, &vsize) != kOk) return Fail(kUnsupported, "ef_search does not fit in shared memory");
+  SearchParams p;
+  p.g = View();
+  p.queries = d_q;
+  p.nq = nq;
+  p.topk = topk;
+  p.ef = ef;
+  p.vsize = vsize;
+  p.smem_per_warp = 0;
+  p.labels = labelled_ ? labels_d_.get() : nullptr;
+  p.out_ids = d_nns;
+  p.out_dist = d_dist;
+  p.out_found = d_found;
+  p.ticket = counters_.get();
+  p.stats = stats_on_ ? counters_.get() + 4 : nullptr;
+  CU(launch_search(p, sm_count_, stream_));
+  return kOk;
+}
+
+int Engine::SearchGraph(const float* q, long long nq, int topk, int ef, int* nns, float* dist, int* found) {
+  if (!has_graph_) return Fail(kBadState, "no graph: call build_graph() or load_index() first");
+  if (nq < 0 || topk < 1) return Fail(kInvalidArgument, "need num_queries >= 0 and topk >= 1");
+  if (nq == 0) return kOk;
+  if (!q || !nns || !dist || !found) return Fail(kInvalidArgument, "null buffer");
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  CU(q_d_.reserve((size_t)nq * d_));
+  CU(ids_d_.reserve((size_t)nq * topk));
+  CU(dist_d_.reserve((size_t)nq * topk));
+  CU(found_d_.reserve((size_t)nq));
+  CU(cudaMemcpyAsync(q_d_.get(), q, (size_t)nq * d_ * sizeof(float), cudaMemcpyHostToDevice, stream_));
+  rc = SearchGraphDevice(q_d_.get(), nq, topk, ef, ids_d_.get(), dist_d_.get(), found_d_.get());
+  if (rc) return rc;
+  CU(cudaMemcpyAsync(nns, ids_d_.get(), (size_t)nq * topk * sizeof(int), cudaMemcpyDeviceToHost, stream_));
+  CU(cudaMemcpyAsync(dist, dist_d_.get(), (size_t)nq * topk * sizeof(float), cudaMemcpyDeviceToHost, stream_));
+  CU(cudaMemcpyAsync(found, found_d_.get(), (size_t)nq * sizeof(int), cudaMemcpyDeviceToHost, stream_));
+  CU(cudaStreamSynchronize(stream_));
+  return kOk;
+}
+
+int Engine::BatchDistance(const int* src, const int* dst, long long npairs, float* out) {
+  if (!has_data_) return Fail(kBadState, "set_data() must be called first");
+  if (npairs < 0 || (npairs > 0 && (!src || !dst || !out))) return Fail(kInvalidArgument, "bad pair list");
+  for (long long i = 0; i < npairs; ++i)
+    if (src[i] < 0 || src[i] >= n_ || dst[i] < 0 || dst[i] >= n_) return Fail(kInvalidArgument, "row id out of range");
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  if (npairs == 0) return kOk;
+  DevBuf<int> s, t;
+  DevBuf<float> o;
+  CU(s.alloc((size_t)npairs));
+  CU(t.alloc((size_t)npairs));
+  CU(o.alloc((size_t)npairs));
+  CU(cudaMemcpyAsync(s.get(), src, (size_t)npairs * sizeof(int), cudaMemcpyHostToDevice, stream_));
+  CU(cudaMemcpyAsync(t.get(), dst, (size_t)npairs * sizeof(int), cudaMemcpyHostToDevice, stream_));
+  GraphView g = View();
+  CU(launch_batch_distance(g, s.get(), t.get(), npairs, o.get(), stream_));
+  CU(cudaMemcpyAsync(out, o.get(), (size_t)npairs * sizeof(float), cudaMemcpyDeviceToHost, stream_));
+  CU(cudaStreamSynchronize(stream_));
+  return kOk;
+}
+
+int Engine::EnableStats(int on) {
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  stats_on_ = on != 0;
+  CU(cudaMemsetAsync(counters_.get() + 4, 0, 4 * sizeof(unsigned long long), stream_));
+  return kOk;
+}
+
+int Engine::GetStats(unsigned long long* out4) {
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  CU(cudaStreamSynchronize(stream_));
+  CU(cudaMemcpy(out4, counters_.get() + 4, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+  CU(cudaMemset(counters_.get() + 4, 0, 4 * sizeof(unsigned long long)));
+  return kOk;
+}
+
+int Engine::Describe(long long* out8) {
+  out8[0] = n_;
+  out8[1] = d_;
+  out8[2] = max_level_;
+  out8[3] = enter_point_;
+  out8[4] = opt_.max_m;
+  out8[5] = opt_.max_m0;
+  out8[6] = total_upper_;
+  out8[7] = sm_count_;
+  return kOk;
+}
+
+int Engine::GetGraph(int* levels, int* rows0, int* rows_upper) {
+  if (!has_levels_ && !has_graph_) return Fail(kBadState, "no graph");
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  CU(cudaStreamSynchronize(stream_));
+  if (levels) std::memcpy(levels, levels_h_.data(), (size_t)n_ * sizeof(int));
+  if (rows0 && n_ > 0)
+    CU(cudaMemcpy2D(rows0, (size_t)opt_.max_m0 * sizeof(int), rows0_.get(), (size_t)stride0_ * sizeof(int),
+                    (size_t)opt_.max_m0 * sizeof(int), (size_t)n_, cudaMemcpyDeviceToHost));
+  if (rows_upper && total_upper_ > 0)
+    CU(cudaMemcpy2D(rows_upper, (size_t)opt_.max_m * sizeof(int), rowsU_.get(), (size_t)strideU_ * sizeof(int),
+                    (size_t)opt_.max_m * sizeof(int), (size_t)total_upper_, cudaMemcpyDeviceToHost));
+  return kOk;
+}
+
+// ---------------------------------------------------------------------------
+// hnswlib-compatible file (layout: cpp/src/cuhnsw_base.cu:159-247 / 250-365)
+// ---------------------------------------------------------------------------
+int Engine::SaveIndex(const char* path) {
+  if (!has_graph_) return Fail(kBadState, "no graph to save");
+  if (!path) return Fail(kInvalidArgument, "null path");
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  CU(cudaStreamSynchronize(stream_));
+  std::FILE* f = std::fopen(path, "wb");
+  if (!f) return Fail(kIoError, std::string("cannot open ") + path + " for writing");
+  const int m = opt_.max_m, m0 = opt_.max_m0;
+  const size_t rec = 4 + 4 * (size_t)m0 + 4 * (size_t)d_ + 8;
+  FileHeader h;
+  h.offset_level0 = 0;
+  h.max_elements = (uint64_t)n_;
+  h.cur_element_count = (uint64_t)n_;
+  h.size_data_per_element = rec;
+  h.label_offset = 4 + 4 * (size_t)m0 + 4 * (size_t)d_;
+  h.offset_data = 4 + 4 * (size_t)m0;
+  h.maxlevel = max_level_;
+  h.enterpoint_node = (uint32_t)enter_point_;
+  h.max_m = (uint64_t)m;
+  h.max_m0 = (uint64_t)m0;
+  h.m = (uint64_t)m;
+  h.mult = opt_.level_mult;
+  h.ef_construction = (uint64_t)opt_.ef_construction;
+  bool ok = std::fwrite(&h, sizeof(h), 1, f) == 1;
+  // level-0 records, in chunks of rows
+  const long long chunk = std::max<long long>(1, (32ll << 20) / (long long)rec);
+  std::vector<int> rows((size_t)std::min(chunk, std::max<long long>(n_, 1)) * stride0_);
+  std::vector<float> vecs((size_t)std::min(chunk, std::max<long long>(n_, 1)) * vstride_);
+  std::vector<unsigned char> out((size_t)std::min(chunk, std::max<long long>(n_, 1)) * rec);
+  for (long long s = 0; s < n_ && ok; s += chunk) {
+    const long long r = std::min(chunk, n_ - s);
+    CU(cudaMemcpy(rows.data(), rows0_.get() + (size_t)s * stride0_, (size_t)r * stride0_ * sizeof(int),
+                  cudaMemcpyDeviceToHost));
+    CU(cudaMemcpy(vecs.data(), vec_.get() + (size_t)s * vstride_, (size_t)r * vstride_ * sizeof(float),
+                  cudaMemcpyDeviceToHost));
+    std::memset(out.data(), 0, (size_t)r * rec);
+    for (long long i = 0; i < r; ++i) {
+      unsigned char* o = out.data() + (size_t)i * rec;
+      const int* row = rows.data() + (size_t)i * stride0_;
+      uint32_t deg = 0;
+      for (int j = 0; j < m0; ++j)
+        if (row[j] >= 0) {
+          uint32_t id = (uint32_t)row[j];
+          std::memcpy(o + 4 + 4 * (size_t)deg, &id, 4);
+          ++deg;
+        }
+      std::memcpy(o, &deg, 4);
+      std::memcpy(o + 4 + 4 * (size_t)m0, vecs.data() + (size_t)i * vstride_, 4 * (size_t)d_);
+      uint64_t label = labelled_ ? (uint64_t)labels_h_[(size_t)(s + i)] : (uint64_t)(s + i);
+      std::memcpy(o + rec - 8, &label, 8);
+    }
+    ok = std::fwrite(out.data(), rec, (size_t)r, f) == (size_t)r;
+  }
+  // upper-layer link lists
+  std::vector<int> upper((size_t)std::max<long long>(total_upper_, 1) * strideU_);
+  if (total_upper_ > 0)
+    CU(cudaMemcpy(upper.data(), rowsU_.get(), (size_t)total_upper_ * strideU_ * sizeof(int), cudaMemcpyDeviceToHost));
+  const size_t per_link = 4 + 4 * (size_t)m;
+  std::vector<unsigned char> lbuf;
+  for (long long i = 0; i < n_ && ok; ++i) {
+    const int lv = levels_h_[(size_t)i];
+    uint32_t nbytes = (uint32_t)(per_link * (size_t)lv);
+    lbuf.assign(4 + (size_t)nbytes, 0);
+    std::memcpy(lbuf.data(), &nbytes, 4);
+    for (int l = 0; l < lv; ++l) {
+      const int* row = upper.data() + ((size_t)upper_base_h_[(size_t)i] + l) * strideU_;
+      unsigned char* o = lbuf.data() + 4 + per_link * (size_t)l;
+      uint32_t deg = 0;
+      for (int j = 0; j < m; ++j)
+        if (row[j] >= 0) {
+          uint32_t id = (uint32_t)row[j];
+          std::memcpy(o + 4 + 4 * (size_t)deg, &id, 4);
+          ++deg;
+        }
+      std::memcpy(o, &deg, 4);
+    }
+    ok = std::fwrite(lbuf.data(), 1, lbuf.size(), f) == lbuf.size();
+  }
+  ok = (std::fclose(f) == 0) && ok;
+  if (!ok) return Fail(kIoError, std::string("short write to ") + path);
+  Log(3, "saved index to %s", path);
+  return kOk;
+}
+
+int Engine::LoadIndex(const char* path) {
+  if (!inited_) return Fail(kBadState, "init() must be called first");
+  if (!path) return Fail(kInvalidArgument, "null path");
+  std::FILE* f = std::fopen(path, "rb");
+  if (!f) return Fail(kIoError, std::string("cannot open ") + path);
+  struct Closer {
+    std::FILE* f;
+    ~Closer() { std::fclose(f); }
+  } closer{f};
+  std::fseek(f, 0, SEEK_END);
+  const long long fsize = std::ftell(f);
+  std::fseek(f, 0, SEEK_SET);
+  FileHeader h;
+  if (fsize < (long long)sizeof(h) || std::fread(&h, sizeof(h), 1, f) != 1)
+    return Fail(kIoError, "index file is shorter than its header");
+  if (h.max_m0 < 1 || h.max_m0 > (uint64_t)kMaxLinksHost || h.max_m < 1 || h.max_m > h.max_m0)
+    return Fail(kUnsupported, "index file: need 1 <= maxM <= maxM0 <= 64");
+  if (h.offset_data != 4 + 4 * h.max_m0 || h.label_offset < h.offset_data || (h.label_offset - h.offset_data) % 4 ||
+      h.size_data_per_element != h.label_offset + 8)
+    return Fail(kParseError, "index file: inconsistent record layout");
+  const long long n = (long long)h.cur_element_count;
+  const int d = (int)((h.label_offset - h.offset_data) / 4);
+  const size_t rec = (size_t)h.size_data_per_element;
+  if (d < 1 || n < 0 || n >= (1ll << 31) - 1) return Fail(kParseError, "index file: bad element count or dimension");
+  if ((long long)sizeof(h) + n * (long long)rec > fsize) return Fail(kIoError, "index file: truncated level-0 block");
+  if (n > 0 && (h.enterpoint_node >= (uint64_t)n || h.maxlevel < 0 || h.maxlevel > 64))
+    return Fail(kParseError, "index file: bad enter point or level");
+  const int m = (int)h.max_m, m0 = (int)h.max_m0;
+  // options that the file overrides (cpp/src/cuhnsw_base.cu:279-285)
+  opt_.max_m = m;
+  opt_.max_m0 = m0;
+  opt_.ef_construction = (int)std::min<uint64_t>(h.ef_construction, kMaxEf);
+  opt_.level_mult = h.mult;
+
+  const int stride0 = round_up(m0, 8);
+  std::vector<float> vecs((size_t)n * d);
+  std::vector<int> rows0((size_t)n * stride0, -1);
+  std::vector<long long> labels((size_t)n);
+  {
+    const long long chunk = std::max<long long>(1, (32ll << 20) / (long long)rec);
+    std::vector<unsigned char> buf((size_t)std::min(chunk, std::max<long long>(n, 1)) * rec);
+    for (long long s = 0; s < n; s += chunk) {
+      const long long r = std::min(chunk, n - s);
+      if (std::fread(buf.data(), rec, (size_t)r, f) != (size_t)r) return Fail(kIoError, "index file: short read");
+      for (long long i = 0; i < r; ++i) {
+        const unsigned char* o = buf.data() + (size_t)i * rec;
+        uint32_t deg;
+        std::memcpy(&deg, o, 4);
+        deg &= 0xffffu;  // hnswlib keeps flags in the upper half of this word
+        if (deg > (uint32_t)m0) return Fail(kParseError, "index file: degree above maxM0");
+        int* row = rows0.data() + (size_t)(s + i) * stride0;
+        for (uint32_t j = 0; j < deg; ++j) {
+          uint32_t id;
+          std::memcpy(&id, o + 4 + 4 * (size_t)j, 4);
+          if (id >= (uint64_t)n) return Fail(kParseError, "index file: neighbour id out of range");
+          row[j] = (int)id;
+        }
+        std::memcpy(vecs.data() + (size_t)(s + i) * d, o + 4 + 4 * (size_t)m0, 4 * (size_t)d);
+        uint64_t label;
+        std::memcpy(&label, o + rec - 8, 8);
+        labels[(size_t)(s + i)] = (long long)label;
+      }
+    }
+  }
+  // upper layers
+  const size_t per_link = 4 + 4 * (size_t)m;
+  std::vector<int> levels((size_t)n, 0);
+  std::vector<std::vector<unsigned char>> lists((size_t)n);
+  for (long long i = 0; i < n; ++i) {
+    uint32_t nbytes;
+    if (std::fread(&nbytes, 4, 1, f) != 1) return Fail(kIoError, "index file: truncated link lists");
+    if (nbytes % per_link || nbytes / per_link > 64) return Fail(kParseError, "index file: bad link list size");
+    levels[(size_t)i] = (int)(nbytes / per_link);
+    if (nbytes) {
+      lists[(size_t)i].resize(nbytes);
+      if (std::fread(lists[(size_t)i].data(), 1, nbytes, f) != nbytes)
+        return Fail(kIoError, "index file: truncated link lists");
+    }
+  }
+  int rc = SetData(vecs.data(), n, d);
+  if (rc) return rc;
+  levels_h_ = levels;
+  max_level_ = h.maxlevel;
+  enter_point_ = n > 0 ? (int)h.enterpoint_node : 0;
+  if (n > 0 && levels[(size_t)enter_point_] < max_level_)
+    return Fail(kParseError, "index file: enter point does not reach the top level");
+  rc = AllocGraph();
+  if (rc) return rc;
+  std::vector<int> rowsU((size_t)std::max<long long>(total_upper_, 1) * strideU_, -1);
+  for (long long i = 0; i < n; ++i) {
+    for (int l = 0; l < levels[(size_t)i]; ++l) {
+      const unsigned char* o = lists[(size_t)i].data() + per_link * (size_t)l;
+      uint32_t deg;
+      std::memcpy(&deg, o, 4);
+      deg &= 0xffffu;
+      if (deg > (uint32_t)m) return Fail(kParseError, "index file: degree above maxM");
+      int* row = rowsU.data() + ((size_t)upper_base_h_[(size_t)i] + l) * strideU_;
+      for (uint32_t j = 0; j < deg; ++j) {
+        uint32_t id;
+        std::memcpy(&id, o + 4 + 4 * (size_t)j, 4);
+        if (id >= (uint64_t)n || levels[id] < l + 1) return Fail(kParseError, "index file: bad upper-layer neighbour");
+        row[j] = (int)id;
+      }
+    }
+  }
+  if (n > 0) {
+    CU(cudaMemcpy(rows0_.get(), rows0.data(), rows0.size() * sizeof(int), cudaMemcpyHostToDevice));
+    if (total_upper_ > 0)
+      CU(cudaMemcpy(rowsU_.get(), rowsU.data(), (size_t)total_upper_ * strideU_ * sizeof(int), cudaMemcpyHostToDevice));
+    std::vector<int> lab32((size_t)n);
+    for (long long i = 0; i < n; ++i) lab32[(size_t)i] = (int)labels[(size_t)i];  // cuhnsw_base.cu:322-324
+    CU(labels_d_.alloc((size_t)n));
+    CU(cudaMemcpy(labels_d_.get(), lab32.data(), (size_t)n * sizeof(int), cudaMemcpyHostToDevice));
+  }
+  labels_h_ = labels;
+  labelled_ = true;
+  has_levels_ = true;
+  has_graph_ = true;
+  Log(3, "loaded %s: num_data %lld, num_dims %d, max_m %d, max_m0 %d, enter_point %d, max_level %d", path, n_, d_, m,
+      m0, enter_point_, max_level_);
+  return kOk;
+}
+
+}  // namespace hnsw

@@ -1,0 +1,147 @@
+// Host layer of the engine: options, device-resident index, level orchestration,
+// hnswlib-format file I/O.  Mirrors the public methods of the reference's host
+// class (cpp/include/cuhnsw.hpp:50-113) but keeps the whole index in flat device
+// arrays instead of per-level host adjacency lists (cpp/include/level_graph.hpp).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "kernels.h"
+
+namespace hnsw {
+
+enum Status {
+  kOk = 0,
+  kInvalidArgument = -1,
+  kIoError = -2,
+  kParseError = -3,
+  kInvalidOption = -4,
+  kCudaError = -5,
+  kBadState = -6,
+  kUnsupported = -7,
+};
+
+// Field names and defaults follow cuhnsw/proto/config.proto:9-27.
+struct Options {
+  int seed = 777;
+  int c_log_level = 2;
+  int max_m = 12;
+  int max_m0 = 24;
+  int ef_construction = 150;
+  double level_mult = 0.0;
+  bool save_remains = false;
+  double hyper_threads = 10.0;
+  int block_dim = 32;
+  std::string dist_type = "dot";
+  int visited_table_size = 0;
+  int visited_list_size = 8192;
+  bool nrz = false;
+  bool reverse_cand = false;
+  double heuristic_coef = 0.25;
+  // extensions (absent from the reference's schema; optional keys of the option file)
+  long long batch_max = 0;  // nodes per insertion batch; 0 = hyper_threads * (SMs * 128 / block_dim)
+  long long ramp_div = 16;  // a batch never exceeds (already linked nodes) / ramp_div
+  int device_id = -1;       // -1 = current device
+};
+
+template <class T>
+class DevBuf {
+ public:
+  DevBuf() = default;
+  DevBuf(const DevBuf&) = delete;
+  DevBuf& operator=(const DevBuf&) = delete;
+  ~DevBuf() { release(); }
+  void release() {
+    if (p_) cudaFree(p_);
+    p_ = nullptr;
+    n_ = 0;
+  }
+  cudaError_t alloc(size_t n) {
+    release();
+    if (n == 0) return cudaSuccess;
+    cudaError_t e = cudaMalloc(&p_, n * sizeof(T));
+    if (e == cudaSuccess) n_ = n;
+    else p_ = nullptr;
+    return e;
+  }
+  cudaError_t reserve(size_t n) { return n <= n_ ? cudaSuccess : alloc(n); }
+  T* get() const { return p_; }
+  size_t size() const { return n_; }
+
+ private:
+  T* p_ = nullptr;
+  size_t n_ = 0;
+};
+
+class Engine {
+ public:
+  Engine();
+  ~Engine();
+
+  int Init(const char* opt_path);
+  int SetData(const float* data, long long num_data, int num_dims);
+  int SetRandomLevels(const int* levels);
+  int BuildGraph();
+  int SaveIndex(const char* path);
+  int LoadIndex(const char* path);
+  // host buffers in, host buffers out; blocks until the results are in place
+  int SearchGraph(const float* qdata, long long num_queries, int topk, int ef_search, int* nns, float* distances,
+                  int* found_cnt);
+  // device buffers in/out; enqueued on the engine's stream, returns without waiting
+  int SearchGraphDevice(const float* d_qdata, long long num_queries, int topk, int ef_search, int* d_nns,
+                        float* d_distances, int* d_found_cnt);
+  // distances between stored rows (host index arrays, host output)
+  int BatchDistance(const int* src, const int* dst, long long npairs, float* out);
+  int SetStream(void* stream);
+  int Synchronize();
+  int EnableStats(int on);
+  int GetStats(unsigned long long* out4);
+  int GetGraph(int* levels, int* rows0, int* rows_upper);  // host copies, for tests
+  int Describe(long long* out8);
+  double last_build_seconds() const { return last_build_seconds_; }
+  const char* last_error() const { return err_.c_str(); }
+  const Options& options() const { return opt_; }
+
+ private:
+  int Fail(int code, const std::string& msg);
+  int FailCuda(cudaError_t e, const char* what);
+  int EnsureDevice();
+  int AllocGraph();
+  int ResolveVsize(int requested_cap, int* vsize) const;
+  GraphView View() const;
+  void Log(int level, const char* fmt, ...) const;
+
+  Options opt_;
+  bool inited_ = false;
+  std::string err_;
+  int device_ = -1;
+  int sm_count_ = 0;
+  size_t smem_optin_ = 0;
+  cudaStream_t stream_ = nullptr;  // legacy default stream unless SetStream is called
+
+  long long n_ = 0;
+  int d_ = 0;
+  int vstride_ = 0;
+  int dist_type_ = 0;
+  int stride0_ = 0, strideU_ = 0;
+  int max_level_ = 0, enter_point_ = 0;
+  long long total_upper_ = 0;
+  bool has_data_ = false, has_levels_ = false, has_graph_ = false, labelled_ = false;
+  std::vector<int> levels_h_;
+  std::vector<int> upper_base_h_;
+  std::vector<long long> labels_h_;
+
+  DevBuf<float> vec_;
+  DevBuf<int> rows0_, rowsU_, levels_d_, upper_base_d_, labels_d_;
+  DevBuf<unsigned long long> counters_;  // [0] search ticket, [1..2] build tickets, [4..7] stats
+  bool stats_on_ = false;
+  // grow-only staging for the host-pointer search path
+  DevBuf<float> q_d_, dist_d_;
+  DevBuf<int> ids_d_, found_d_;
+  double last_build_seconds_ = 0.0;
+};
+
+}  // namespace hnsw

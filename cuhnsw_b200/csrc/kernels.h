@@ -1,0 +1,90 @@
+// Host-visible parameter blocks and launchers of the CUDA kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace hnsw {
+
+// Device-resident index.  All ids are global node ids on every layer.
+struct GraphView {
+  const float* vec;       // n x vstride, rows zero padded, 32-byte aligned rows
+  int vstride;            // floats per row (multiple of 8)
+  int d;
+  int dist_type;          // 0 dot (-dot), 1 l2 (squared)
+  long long n;
+  int* rows0;             // n x stride0, -1 padded
+  int stride0;            // ints per layer-0 row (multiple of 8, >= max_m0)
+  int* rowsU;             // total_upper x strideU, -1 padded
+  int strideU;
+  const int* upper_base;  // n: index of a node's layer-1 row in rowsU (exclusive prefix sum of levels)
+  int max_level;
+  int enter_point;
+};
+
+struct SearchParams {
+  GraphView g;
+  const float* queries;  // nq x d, unpadded
+  long long nq;
+  int topk;
+  int ef;
+  int vsize;             // visited table entries per warp (power of two)
+  int smem_per_warp;     // filled by the launcher
+  const int* labels;     // optional id -> label map (index loaded from a file)
+  int* out_ids;          // nq x topk
+  float* out_dist;       // nq x topk
+  int* out_found;        // nq
+  unsigned long long* ticket;  // work counter (zeroed by the launcher)
+  unsigned long long* stats;   // optional: evals, expansions, sweeps, inserts
+};
+
+cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream);
+size_t search_smem_per_cta(int d, int ef, int vsize);
+
+// ---- construction -------------------------------------------------------
+struct BuildLevel {
+  GraphView g;           // rows of the level being built are read through rows/stride below
+  int level;
+  int* rows;             // this level's adjacency table (rows0 or rowsU view)
+  float* dists;          // stored edge distances, same shape as rows
+  const float* distU;    // distance table of the upper layers (source when a row is copied down)
+  int stride;            // ints per row of this level
+  int max_m;             // link budget of this level (max_m0 on level 0)
+  const int* levels;     // n
+  const int* nodes;      // node list of the level, ascending ids (nullptr on level 0: identity)
+  long long n_level;
+  unsigned char* went;   // n: row has been through neighbour selection on this level
+  int ef_construction;
+  float heuristic_coef;
+  int save_remains;
+  int vsize;
+};
+
+struct BuildScratch {
+  int* st_ids;                  // bmax x stride: staged own rows
+  float* st_dist;
+  unsigned* pkeys;              // bmax x stride proposal keys: target node id (n = none)
+  unsigned* pkeys_sorted;
+  unsigned long long* pvals;    // source node id << 32 | distance bits
+  unsigned long long* pvals_sorted;
+  void* sort_tmp;
+  size_t sort_tmp_bytes;
+  unsigned long long* ticket;   // 2 counters
+  unsigned long long* stats;    // optional
+};
+
+size_t build_sort_tmp_bytes(long long max_items);
+// rows of `level` for every node of the level: copy from the level above or seed with the descent result
+cudaError_t launch_init_level(const BuildLevel& L, unsigned long long* ticket, int sm_count, cudaStream_t stream);
+// one insertion batch: nodes [first, first + count) of the level's node list
+cudaError_t launch_build_batch(const BuildLevel& L, const BuildScratch& S, long long first, int count,
+                               int sm_count, cudaStream_t stream);
+// pads an unpadded n x d matrix into n x vstride rows
+cudaError_t launch_pad_rows(const float* src, float* dst, long long n, int d, int vstride, cudaStream_t stream);
+cudaError_t launch_unpad_rows(const float* src, float* dst, long long n, int d, int vstride, cudaStream_t stream);
+cudaError_t launch_fill_i32(int* p, long long n, int v, cudaStream_t stream);
+// out[i] = canonical distance between stored rows src[i] and dst[i]
+cudaError_t launch_batch_distance(const GraphView& g, const int* src, const int* dst, long long npairs, float* out,
+                                  cudaStream_t stream);
+
+}  // namespace hnsw

@@ -1,0 +1,111 @@
+// Batch kNN search: greedy descent through the upper layers fused with the
+// ef_search-bounded layer-0 search in ONE launch over a device-resident graph.
+//
+// Replaces GetEntryPointsKernel + SearchGraphKernel and their host driver
+// (cpp/include/cuda_search_kernels.cuh:11-165, cpp/src/cuhnsw_build.cu:210-290),
+// which re-flatten and re-upload the graph on every call, launch once per
+// layer and keep the heap in global memory.
+#include "kernels.h"
+#include "beam.cuh"
+
+namespace hnsw {
+
+constexpr int kWarpsPerCta = 2;
+
+template <class Dist>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+search_kernel(SearchParams p) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned char* mine = smem + (size_t)warp * p.smem_per_warp;
+  Dist de;
+  VecTable tab{reinterpret_cast<const float4*>(p.g.vec), p.g.vstride / 4, (p.g.d + 3) / 4, p.g.d, p.g.dist_type};
+  de.init(tab, mine);
+  WarpList wl;
+  wl.bind(mine + Dist::smem_bytes(p.g.d), p.ef, p.vsize);
+  WalkCounters wc{0, 0, 0, 0};
+
+  for (;;) {
+    long long qi = 0;
+    if (lane == 0) qi = (long long)atomicAdd(p.ticket, 1ull);
+    qi = __shfl_sync(FULL, qi, 0);
+    if (qi >= p.nq) break;
+    de.load_query(p.queries + (size_t)qi * p.g.d);
+    wl.reset();
+    int cur = p.g.enter_point;
+    float dcur = de.eval(cur, 1);
+    dcur = __shfl_sync(FULL, dcur, 0);
+    wc.evals += 1;
+    greedy_descent(de, wl.spos, p.g.rowsU, p.g.strideU, p.g.upper_base, p.g.max_level, 0, cur, dcur, wc);
+    // layer 0: list = {entry}, visited = {entry} (cuda_search_kernels.cuh:108-112)
+    if (lane == 0) wl.keys[0] = mkkey(dcur, cur);
+    wl.size = 1;
+    wl.cursor = 0;
+    wl.mark(cur);
+    beam_layer(de, wl, p.g.rows0, p.g.stride0, p.g.upper_base, 0, -1, wc);
+    // ascending top-k, found = min(size, k); slots past `found` read -1 / +inf
+    int found = min(wl.size, p.topk);
+    for (int j = lane; j < p.topk; j += 32) {
+      int id = -1;
+      float dist = __int_as_float(0x7f800000);
+      if (j < found) {
+        unsigned long long k = wl.keys[j];
+        id = key_id(k);
+        dist = key_dist(k);
+        if (p.labels) id = __ldg(p.labels + id);
+      }
+      p.out_ids[(size_t)qi * p.topk + j] = id;
+      p.out_dist[(size_t)qi * p.topk + j] = dist;
+    }
+    if (lane == 0) p.out_found[qi] = found;
+    __syncwarp();
+  }
+  if (p.stats && lane == 0) {
+    atomicAdd(p.stats + 0, wc.evals);
+    atomicAdd(p.stats + 1, wc.expansions);
+    atomicAdd(p.stats + 2, wc.sweeps);
+    atomicAdd(p.stats + 3, wc.inserts);
+  }
+}
+
+template <class Dist>
+static cudaError_t launch_search_t(const SearchParams& p0, int sm_count, cudaStream_t stream) {
+  SearchParams p = p0;
+  size_t per_warp = Dist::smem_bytes(p.g.d) + WarpList::smem_bytes(p.ef, p.vsize);
+  per_warp = (per_warp + 15) / 16 * 16;
+  p.smem_per_warp = (int)per_warp;
+  size_t smem = per_warp * kWarpsPerCta;
+  auto kern = search_kernel<Dist>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  int per_sm = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kWarpsPerCta * 32, smem);
+  if (e != cudaSuccess) return e;
+  if (per_sm < 1) return cudaErrorInvalidConfiguration;
+  long long want = (p.nq + kWarpsPerCta - 1) / kWarpsPerCta;
+  long long grid = (long long)per_sm * sm_count;
+  if (grid > want) grid = want;
+  if (grid < 1) grid = 1;
+  e = cudaMemsetAsync(p.ticket, 0, sizeof(unsigned long long), stream);
+  if (e != cudaSuccess) return e;
+  kern<<<(unsigned)grid, kWarpsPerCta * 32, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+size_t search_smem_per_cta(int d, int ef, int vsize) {
+  size_t dq = d <= 128 ? 0 : DistLarge::smem_bytes(d);
+  size_t per_warp = (dq + WarpList::smem_bytes(ef, vsize) + 15) / 16 * 16;
+  return per_warp * kWarpsPerCta;
+}
+
+cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream) {
+  if (p.nq <= 0) return cudaSuccess;
+  const int d = p.g.d;
+  if (d <= 32) return launch_search_t<DistSmall<1>>(p, sm_count, stream);
+  if (d <= 64) return launch_search_t<DistSmall<2>>(p, sm_count, stream);
+  if (d <= 96) return launch_search_t<DistSmall<3>>(p, sm_count, stream);
+  if (d <= 128) return launch_search_t<DistSmall<4>>(p, sm_count, stream);
+  return launch_search_t<DistLarge>(p, sm_count, stream);
+}
+
+}  // namespace hnsw

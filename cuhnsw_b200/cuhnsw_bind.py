@@ -1,0 +1,178 @@
+"""``CuHNSWBind``: the binding class of the reference (cuhnsw/bindings.cc:18-94),
+re-expressed over the C ABI of libcuhnsw_b200.so with ctypes.
+
+Same method names, argument meaning and error behaviour: ``init`` returns a
+bool; every other failure raises ``RuntimeError`` (pybind11 turns the
+reference's ``std::runtime_error`` into exactly that).  There is no CPU
+fallback: if the shared library is missing, importing this module fails.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libcuhnsw_b200.so")
+
+_f32p = ctypes.POINTER(ctypes.c_float)
+_i32p = ctypes.POINTER(ctypes.c_int32)
+
+# name -> (restype, argtypes); must list every symbol include/cuhnsw_b200.h declares
+SIGNATURES = {
+  "cuhnsw_create": (ctypes.c_void_p, []),
+  "cuhnsw_destroy": (None, [ctypes.c_void_p]),
+  "cuhnsw_last_error": (ctypes.c_char_p, [ctypes.c_void_p]),
+  "cuhnsw_init": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p]),
+  "cuhnsw_set_data": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32]),
+  "cuhnsw_set_random_levels": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_build_graph": (ctypes.c_int, [ctypes.c_void_p]),
+  "cuhnsw_save_index": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p]),
+  "cuhnsw_load_index": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p]),
+  "cuhnsw_search_knn": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
+                                       ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_search_knn_device": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
+                                              ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_batch_distance": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                            ctypes.c_void_p]),
+  "cuhnsw_set_stream": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_synchronize": (ctypes.c_int, [ctypes.c_void_p]),
+  "cuhnsw_enable_stats": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32]),
+  "cuhnsw_get_stats": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_describe": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_get_graph": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_last_build_seconds": (ctypes.c_double, [ctypes.c_void_p]),
+}
+
+_lib = None
+
+
+def load_library():
+  global _lib
+  if _lib is None:
+    if not os.path.exists(LIB_PATH):
+      raise ImportError(f"{LIB_PATH} is missing: build it with `make -C {os.path.join(_HERE, 'csrc')}` "
+                        "(the engine has no CPU fallback)")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+      fn = getattr(lib, name)
+      fn.restype = res
+      fn.argtypes = args
+    _lib = lib
+  return _lib
+
+
+IO_ERROR, PARSE_ERROR = -2, -3
+
+
+class CuHNSWBind:
+  def __init__(self):
+    self._lib = load_library()
+    self._h = self._lib.cuhnsw_create()
+    if not self._h:
+      raise RuntimeError("cuhnsw_create failed")
+
+  def __del__(self):
+    h, self._h = getattr(self, "_h", None), None
+    if h:
+      self._lib.cuhnsw_destroy(h)
+
+  def __repr__(self):
+    return "<CuHNSWBind>"
+
+  def _check(self, rc):
+    if rc != 0:
+      raise RuntimeError(self._lib.cuhnsw_last_error(self._h).decode("utf8", "replace"))
+
+  # -- methods of the reference binding -------------------------------------
+  def init(self, opt_path):
+    if isinstance(opt_path, str):
+      opt_path = opt_path.encode("utf8")
+    rc = self._lib.cuhnsw_init(self._h, opt_path)
+    if rc in (IO_ERROR, PARSE_ERROR):
+      return False
+    self._check(rc)
+    return True
+
+  def set_data(self, data):
+    arr = np.ascontiguousarray(data, dtype=np.float32)
+    if arr.ndim != 2:
+      raise RuntimeError("data must be 2d array")
+    self._check(self._lib.cuhnsw_set_data(self._h, arr.ctypes.data, arr.shape[0], arr.shape[1]))
+
+  def set_random_levels(self, levels):
+    arr = np.ascontiguousarray(levels, dtype=np.int32)
+    if arr.ndim != 1:
+      raise RuntimeError("levels must be 1d array")
+    self._check(self._lib.cuhnsw_set_random_levels(self._h, arr.ctypes.data))
+
+  def build_graph(self):
+    self._check(self._lib.cuhnsw_build_graph(self._h))
+
+  def save_index(self, fpath):
+    if isinstance(fpath, str):
+      fpath = fpath.encode("utf8")
+    self._check(self._lib.cuhnsw_save_index(self._h, fpath))
+
+  def load_index(self, fpath):
+    if isinstance(fpath, str):
+      fpath = fpath.encode("utf8")
+    self._check(self._lib.cuhnsw_load_index(self._h, fpath))
+
+  def search_knn(self, qdata, topk, ef_search, nns, distances, found):
+    q = np.ascontiguousarray(qdata, dtype=np.float32)
+    if q.ndim not in (1, 2):
+      raise RuntimeError("data array must be 1d / 2d shape")
+    nq = 1 if q.ndim == 1 else q.shape[0]
+    for name, arr, dt in (("nns", nns, np.int32), ("distances", distances, np.float32), ("found", found, np.int32)):
+      if not (isinstance(arr, np.ndarray) and arr.dtype == dt and arr.flags.c_contiguous and arr.flags.writeable):
+        raise RuntimeError(f"{name} must be a writable C-contiguous {np.dtype(dt).name} array")
+    if nns.size < nq * topk or distances.size < nq * topk or found.size < nq:
+      raise RuntimeError("output arrays are too small")
+    self._check(self._lib.cuhnsw_search_knn(self._h, q.ctypes.data, nq, topk, ef_search, nns.ctypes.data,
+                                            distances.ctypes.data, found.ctypes.data))
+
+  # -- additions of this engine ---------------------------------------------
+  def search_knn_device(self, q_ptr, nq, topk, ef_search, nns_ptr, dist_ptr, found_ptr):
+    """All arguments are device addresses (ints); enqueued, not waited for."""
+    self._check(self._lib.cuhnsw_search_knn_device(self._h, q_ptr, nq, topk, ef_search, nns_ptr, dist_ptr,
+                                                   found_ptr))
+
+  def batch_distance(self, src, dst):
+    src = np.ascontiguousarray(src, np.int32)
+    dst = np.ascontiguousarray(dst, np.int32)
+    out = np.zeros(src.shape[0], np.float32)
+    self._check(self._lib.cuhnsw_batch_distance(self._h, src.ctypes.data, dst.ctypes.data, src.shape[0],
+                                                out.ctypes.data))
+    return out
+
+  def set_stream(self, stream_ptr):
+    self._check(self._lib.cuhnsw_set_stream(self._h, stream_ptr))
+
+  def synchronize(self):
+    self._check(self._lib.cuhnsw_synchronize(self._h))
+
+  def enable_stats(self, on=True):
+    self._check(self._lib.cuhnsw_enable_stats(self._h, int(bool(on))))
+
+  def get_stats(self):
+    out = np.zeros(4, np.uint64)
+    self._check(self._lib.cuhnsw_get_stats(self._h, out.ctypes.data))
+    return dict(evals=int(out[0]), expansions=int(out[1]), sweeps=int(out[2]), inserts=int(out[3]))
+
+  def describe(self):
+    out = np.zeros(8, np.int64)
+    self._check(self._lib.cuhnsw_describe(self._h, out.ctypes.data))
+    keys = ("num_data", "num_dims", "max_level", "enter_point", "max_m", "max_m0", "upper_rows", "sm_count")
+    return dict(zip(keys, (int(x) for x in out)))
+
+  def get_graph(self):
+    info = self.describe()
+    n = info["num_data"]
+    levels = np.zeros(n, np.int32)
+    rows0 = np.full((n, info["max_m0"]), -1, np.int32)
+    rows_u = np.full((max(info["upper_rows"], 1), info["max_m"]), -1, np.int32)
+    self._check(self._lib.cuhnsw_get_graph(self._h, levels.ctypes.data, rows0.ctypes.data, rows_u.ctypes.data))
+    return levels, rows0, rows_u
+
+  def last_build_seconds(self):
+    return float(self._lib.cuhnsw_last_build_seconds(self._h))

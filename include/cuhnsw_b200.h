@@ -1,0 +1,102 @@
+/*
+ * C ABI of the B200 HNSW engine (libcuhnsw_b200.so).
+ *
+ * Every entry point takes plain pointers and sizes, returns 0 on success and a
+ * negative status otherwise (no C++ exception crosses this boundary); the text
+ * of the last error of a handle is available from cuhnsw_last_error().  The
+ * functions are exactly what a binding of the reference's host class needs:
+ * each one names the reference method it stands for (paths inside the
+ * reference project).  One handle owns one device-resident index on one GPU;
+ * calls on one handle must not overlap.
+ */
+#ifndef CUHNSW_B200_H_
+#define CUHNSW_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cuhnsw_handle cuhnsw_handle;
+
+enum {
+  CUHNSW_OK = 0,
+  CUHNSW_INVALID_ARGUMENT = -1,
+  CUHNSW_IO_ERROR = -2,      /* option or index file cannot be opened / is truncated */
+  CUHNSW_PARSE_ERROR = -3,   /* option file is not valid JSON / index file is inconsistent */
+  CUHNSW_INVALID_OPTION = -4,/* e.g. dist_type other than "dot" or "l2" */
+  CUHNSW_CUDA_ERROR = -5,    /* includes "no CUDA device": there is no CPU path */
+  CUHNSW_BAD_STATE = -6,     /* call order: init -> set_data -> set_random_levels -> build_graph */
+  CUHNSW_UNSUPPORTED = -7
+};
+
+/* CuHNSWBind() constructor + cuhnsw::CuHNSW::CuHNSW()  (cuhnsw/bindings.cc:20, cpp/src/cuhnsw_base.cu:13-62) */
+cuhnsw_handle* cuhnsw_create(void);
+/* destructor (cpp/src/cuhnsw_base.cu:65) */
+void cuhnsw_destroy(cuhnsw_handle* h);
+/* text of the last failure on this handle; valid until the next call on it */
+const char* cuhnsw_last_error(const cuhnsw_handle* h);
+
+/* CuHNSWBind::Init -> CuHNSW::Init(opt_path)  (cuhnsw/bindings.cc:22-24, cpp/src/cuhnsw_base.cu:67-106).
+ * opt_path: JSON object with the field names of cuhnsw/proto/config.proto:9-27.
+ * IO/PARSE errors correspond to the reference returning false; INVALID_OPTION to its runtime_error. */
+int cuhnsw_init(cuhnsw_handle* h, const char* opt_path);
+
+/* CuHNSWBind::SetData -> CuHNSW::SetData  (cuhnsw/bindings.cc:26-33, cpp/src/cuhnsw_base.cu:108-128).
+ * data: num_data x num_dims row-major fp32 on the host; copied, the pointer is not retained. */
+int cuhnsw_set_data(cuhnsw_handle* h, const float* data, int64_t num_data, int32_t num_dims);
+
+/* CuHNSWBind::SetRandomLevels -> CuHNSW::SetRandomLevels  (cuhnsw/bindings.cc:39-44, cpp/src/cuhnsw_base.cu:130-156).
+ * levels: num_data int32, node i belongs to layers 0..levels[i]. */
+int cuhnsw_set_random_levels(cuhnsw_handle* h, const int32_t* levels);
+
+/* CuHNSWBind::BuildGraph -> CuHNSW::BuildGraph  (cuhnsw/bindings.cc:35-37, cpp/src/cuhnsw_build.cu:96-208) */
+int cuhnsw_build_graph(cuhnsw_handle* h);
+
+/* CuHNSWBind::SaveIndex / LoadIndex -> CuHNSW::SaveIndex / LoadIndex
+ * (cuhnsw/bindings.cc:46-52, cpp/src/cuhnsw_base.cu:159-247, 250-365); hnswlib file layout. */
+int cuhnsw_save_index(cuhnsw_handle* h, const char* fpath);
+int cuhnsw_load_index(cuhnsw_handle* h, const char* fpath);
+
+/* CuHNSWBind::SearchGraph -> CuHNSW::SearchGraph  (cuhnsw/bindings.cc:54-68, cpp/src/cuhnsw_build.cu:210-290).
+ * Host buffers: qdata num_queries x num_dims; nns/distances num_queries x topk; found_cnt num_queries.
+ * ef_search is raised to topk.  Distances: squared l2, or -dot.  Rows are ascending by (distance, id);
+ * slots past found_cnt[i] hold -1 / +inf.  Ids are file labels when the index came from load_index. */
+int cuhnsw_search_knn(cuhnsw_handle* h, const float* qdata, int64_t num_queries, int32_t topk, int32_t ef_search,
+                      int32_t* nns, float* distances, int32_t* found_cnt);
+
+/* Same search with every buffer already on the engine's GPU; enqueued on the engine's stream and not
+ * waited for.  Device-resident counterpart of the kernel launch inside CuHNSW::SearchGraph
+ * (cpp/src/cuhnsw_build.cu:254-274) without its per-call copies. */
+int cuhnsw_search_knn_device(cuhnsw_handle* h, const float* d_qdata, int64_t num_queries, int32_t topk,
+                             int32_t ef_search, int32_t* d_nns, float* d_distances, int32_t* d_found_cnt);
+
+/* out[i] = distance between stored rows src[i] and dst[i] (host arrays): squared l2 or -dot, in the engine's
+ * fixed fp32 summation order.  Counterpart of BatchDistanceKernel (cpp/include/cuda_dist_kernels.cuh:143-156). */
+int cuhnsw_batch_distance(cuhnsw_handle* h, const int32_t* src, const int32_t* dst, int64_t num_pairs, float* out);
+
+/* Stream the engine launches on (a cudaStream_t passed as void*); default: the legacy default stream.
+ * The reference launches on the default stream only (cpp/src/cuhnsw_build.cu:66,163,254). */
+int cuhnsw_set_stream(cuhnsw_handle* h, void* cuda_stream);
+/* cudaDeviceSynchronize of the reference (cpp/src/cuhnsw_build.cu:80,185,275), on the engine's stream */
+int cuhnsw_synchronize(cuhnsw_handle* h);
+
+/* Work counters, the counterpart of acc_visited_cnt (cpp/include/cuda_search_kernels.cuh:141-143):
+ * out4 = {rows gathered for a distance, layer rows expanded, greedy sweeps, keys inserted} since the last read. */
+int cuhnsw_enable_stats(cuhnsw_handle* h, int32_t on);
+int cuhnsw_get_stats(cuhnsw_handle* h, uint64_t* out4);
+
+/* out8 = {num_data, num_dims, max_level, enter_point, max_m, max_m0, upper-layer rows, SM count}
+ * (the values CuHNSW::LoadIndex logs, cpp/src/cuhnsw_base.cu:286-287) */
+int cuhnsw_describe(cuhnsw_handle* h, int64_t* out8);
+/* Host copies of the graph, the flat form of LevelGraph (cpp/include/level_graph.hpp:23-89):
+ * levels[num_data]; rows0[num_data x max_m0]; rows_upper[upper rows x max_m], -1 padded; any may be NULL. */
+int cuhnsw_get_graph(cuhnsw_handle* h, int32_t* levels, int32_t* rows0, int32_t* rows_upper);
+/* wall seconds of the last cuhnsw_build_graph */
+double cuhnsw_last_build_seconds(const cuhnsw_handle* h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUHNSW_B200_H_ */

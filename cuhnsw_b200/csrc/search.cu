@@ -14,7 +14,7 @@ constexpr int kWarpsPerCta = 2;
 
 template <class Dist>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
-search_kernel(SearchParams p) {
+knn_search_kernel(SearchParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned char* mine = smem + (size_t)warp * p.smem_per_warp;
@@ -75,7 +75,7 @@ static cudaError_t launch_search_t(const SearchParams& p0, int sm_count, cudaStr
   per_warp = (per_warp + 15) / 16 * 16;
   p.smem_per_warp = (int)per_warp;
   size_t smem = per_warp * kWarpsPerCta;
-  auto kern = search_kernel<Dist>;
+  auto kern = knn_search_kernel<Dist>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   int per_sm = 0;

@@ -94,4 +94,14 @@ int cuhnsw_get_graph(cuhnsw_handle* h, int32_t* levels, int32_t* rows0, int32_t*
 }
 double cuhnsw_last_build_seconds(const cuhnsw_handle* h) { return h ? h->engine.last_build_seconds() : 0.0; }
 
+int cuhnsw_merge_topk_device(const int32_t* d_ids, const float* d_distances, int32_t parts, int64_t num_queries,
+                             int32_t topk, int32_t* d_out_ids, float* d_out_distances, int32_t* d_out_found,
+                             void* cuda_stream) {
+  if (parts < 1 || topk < 1 || num_queries < 0) return CUHNSW_INVALID_ARGUMENT;
+  if (num_queries > 0 && (!d_ids || !d_distances || !d_out_ids || !d_out_distances)) return CUHNSW_INVALID_ARGUMENT;
+  cudaError_t e = hnsw::launch_merge_topk(d_ids, d_distances, parts, num_queries, topk, d_out_ids, d_out_distances,
+                                          d_out_found, reinterpret_cast<cudaStream_t>(cuda_stream));
+  return e == cudaSuccess ? CUHNSW_OK : CUHNSW_CUDA_ERROR;
+}
+
 }  // extern "C"

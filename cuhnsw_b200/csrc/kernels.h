@@ -83,6 +83,9 @@ cudaError_t launch_build_batch(const BuildLevel& L, const BuildScratch& S, long 
 cudaError_t launch_pad_rows(const float* src, float* dst, long long n, int d, int vstride, cudaStream_t stream);
 cudaError_t launch_unpad_rows(const float* src, float* dst, long long n, int d, int vstride, cudaStream_t stream);
 cudaError_t launch_fill_i32(int* p, long long n, int v, cudaStream_t stream);
+// merges parts x nq x k per-shard rows (global ids, -1 = empty) into nq x k rows ordered by (distance, id)
+cudaError_t launch_merge_topk(const int* ids, const float* dist, int parts, long long nq, int k, int* out_ids,
+                              float* out_dist, int* out_found, cudaStream_t stream);
 // out[i] = canonical distance between stored rows src[i] and dst[i]
 cudaError_t launch_batch_distance(const GraphView& g, const int* src, const int* dst, long long npairs, float* out,
                                   cudaStream_t stream);

@@ -41,6 +41,9 @@ SIGNATURES = {
   "cuhnsw_describe": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
   "cuhnsw_get_graph": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
   "cuhnsw_last_build_seconds": (ctypes.c_double, [ctypes.c_void_p]),
+  "cuhnsw_merge_topk_device": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64,
+                                               ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                               ctypes.c_void_p]),
 }
 
 _lib = None

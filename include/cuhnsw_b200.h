@@ -96,6 +96,14 @@ int cuhnsw_get_graph(cuhnsw_handle* h, int32_t* levels, int32_t* rows0, int32_t*
 /* wall seconds of the last cuhnsw_build_graph */
 double cuhnsw_last_build_seconds(const cuhnsw_handle* h);
 
+/* Base-sharded search: merges `parts` per-shard result blocks (d_ids/d_distances: parts x num_queries x topk,
+ * ids already global, -1 = empty slot) into num_queries x topk rows ordered by (distance, id); all device
+ * pointers, enqueued on cuda_stream.  No counterpart in the reference, which is single-device
+ * (README.md:146 there); it consumes the rows cuhnsw_search_knn_device produces on every shard. */
+int cuhnsw_merge_topk_device(const int32_t* d_ids, const float* d_distances, int32_t parts, int64_t num_queries,
+                             int32_t topk, int32_t* d_out_ids, float* d_out_distances, int32_t* d_out_found,
+                             void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -434,6 +434,50 @@ int Engine::SearchGraph(const float* q, long long nq, int topk, int ef, int* nns
   return kOk;
 }
 
+int Engine::SearchGraphStatic(const float* q, long long nq, int topk, int ef, int* nns, float* dist, int* found) {
+  if (!has_graph_) return Fail(kBadState, "no graph: call build_graph() or load_index() first");
+  if (nq < 0 || topk < 1) return Fail(kInvalidArgument, "need num_queries >= 0 and topk >= 1");
+  if (nq == 0) return kOk;
+  if (!q || !nns || !dist || !found) return Fail(kInvalidArgument, "null buffer");
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  ef = std::max(ef, topk);
+  if (ef > kMaxEf) return Fail(kUnsupported, "ef_search above 8192 is not supported");
+  const size_t need = search_static_bytes(nq, d_, topk), cap = search_static_capacity();
+  if (need > cap) {
+    std::ostringstream os;
+    os << "search without allocation: " << nq << " queries x " << d_ << " dims, topk " << topk << " need " << need
+       << " bytes of fixed device scratch, the limit is " << cap << "; split the batch or use cuhnsw_search_knn";
+    return Fail(kInvalidArgument, os.str());
+  }
+  if (n_ == 0) {
+    for (long long i = 0; i < nq; ++i) found[i] = 0;
+    for (long long i = 0; i < nq * topk; ++i) {
+      nns[i] = -1;
+      dist[i] = INFINITY;
+    }
+    return kOk;
+  }
+  int vsize = 0;
+  if (ResolveVsize(ef, &vsize) != kOk) return Fail(kUnsupported, "ef_search does not fit in shared memory");
+  SearchParams p;
+  p.g = View();
+  p.queries = nullptr;
+  p.nq = nq;
+  p.topk = topk;
+  p.ef = ef;
+  p.vsize = vsize;
+  p.smem_per_warp = 0;
+  p.labels = labelled_ ? labels_d_.get() : nullptr;
+  p.out_ids = nullptr;
+  p.out_dist = nullptr;
+  p.out_found = nullptr;
+  p.ticket = nullptr;
+  p.stats = nullptr;
+  CU(search_static(p, q, nns, dist, found, sm_count_, stream_));
+  return kOk;
+}
+
 int Engine::BatchDistance(const int* src, const int* dst, long long npairs, float* out) {
   if (!has_data_) return Fail(kBadState, "set_data() must be called first");
   if (npairs < 0 || (npairs > 0 && (!src || !dst || !out))) return Fail(kInvalidArgument, "bad pair list");

@@ -93,6 +93,9 @@ class Engine {
   // device buffers in/out; enqueued on the engine's stream, returns without waiting
   int SearchGraphDevice(const float* d_qdata, long long num_queries, int topk, int ef_search, int* d_nns,
                         float* d_distances, int* d_found_cnt);
+  // host buffers in/out like SearchGraph, but no allocation: staging lives in a fixed device array
+  int SearchGraphStatic(const float* qdata, long long num_queries, int topk, int ef_search, int* nns,
+                        float* distances, int* found_cnt);
   // distances between stored rows (host index arrays, host output)
   int BatchDistance(const int* src, const int* dst, long long npairs, float* out);
   int SetStream(void* stream);

@@ -40,6 +40,11 @@ struct SearchParams {
 
 cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream);
 size_t search_smem_per_cta(int d, int ef, int vsize);
+// search whose device staging and work ticket live in a fixed file-scope device array (no allocation)
+size_t search_static_capacity();
+size_t search_static_bytes(long long nq, int d, int topk);
+cudaError_t search_static(const SearchParams& proto, const float* h_queries, int* h_ids, float* h_dist, int* h_found,
+                          int sm_count, cudaStream_t stream);
 
 // ---- construction -------------------------------------------------------
 struct BuildLevel {

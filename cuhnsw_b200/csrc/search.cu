@@ -109,3 +109,88 @@ cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stre
 }
 
 }  // namespace hnsw
+
+// ---------------------------------------------------------------------------
+// Search that allocates nothing
+// ---------------------------------------------------------------------------
+// Some callers must not reach cudaMalloc: a serving process that has already handed every free byte of
+// device memory to its own pool allocator (a late cudaMalloc there fails or evicts), a job running under a
+// fixed memory budget, or a real-time loop that cannot take the device-wide synchronisation cudaMalloc and
+// cudaFree imply.  For them the staging buffers and the work ticket of the search kernel live in one
+// file-scope device array of fixed size instead of grow-on-demand allocations.  Every GPU that loads this
+// library carries the array (4 MiB) until the process exits.
+//
+// In host code the name `g_search_scratch` is only the runtime's handle of the symbol, not a device address:
+// a kernel given `g_search_scratch` from the host would fault or, where the GPU can reach host memory, use the
+// wrong memory.  The device address is obtained once per device with cudaGetSymbolAddress (with that device
+// current) and it is that pointer that is handed to the kernel.
+#include <mutex>
+
+namespace hnsw {
+
+constexpr size_t kStaticScratchBytes = 4u << 20;
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) unsigned char g_search_scratch[kStaticScratchBytes];
+
+static std::mutex g_scratch_mu;
+static void* g_scratch_addr[kMaxDevices] = {};
+
+static cudaError_t static_scratch_address(unsigned char** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_search_scratch);  // set-up: first call on this device
+    if (e != cudaSuccess) return e;
+    g_scratch_addr[dev] = p;
+  }
+  *out = static_cast<unsigned char*>(g_scratch_addr[dev]);
+  return cudaSuccess;
+}
+
+static size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+size_t search_static_capacity() { return kStaticScratchBytes; }
+
+size_t search_static_bytes(long long nq, int d, int topk) {
+  return 256 + align256((size_t)nq * d * sizeof(float)) + 2 * align256((size_t)nq * topk * 4) +
+         align256((size_t)nq * sizeof(int));
+}
+
+// Host buffers in and out; the caller has checked search_static_bytes() <= search_static_capacity().
+// Layout of the array: [ticket | queries | ids | distances | found].  Only the ticket has to start at zero and
+// the launcher clears it on the stream; everything else is overwritten before it is read.  The array is shared
+// by every call in the process on this device, so two calls that overlap on the GPU race on it.
+cudaError_t search_static(const SearchParams& proto, const float* h_queries, int* h_ids, float* h_dist, int* h_found,
+                          int sm_count, cudaStream_t stream) {
+  unsigned char* base = nullptr;
+  cudaError_t e = static_scratch_address(&base);
+  if (e != cudaSuccess) return e;
+  const long long nq = proto.nq;
+  const size_t qbytes = (size_t)nq * proto.g.d * sizeof(float), rbytes = (size_t)nq * proto.topk * 4;
+  SearchParams p = proto;
+  p.ticket = reinterpret_cast<unsigned long long*>(base);
+  p.stats = nullptr;
+  unsigned char* at = base + 256;
+  float* d_q = reinterpret_cast<float*>(at);
+  at += align256(qbytes);
+  p.out_ids = reinterpret_cast<int*>(at);
+  at += align256(rbytes);
+  p.out_dist = reinterpret_cast<float*>(at);
+  at += align256(rbytes);
+  p.out_found = reinterpret_cast<int*>(at);
+  p.queries = d_q;
+  if ((e = cudaMemcpyAsync(d_q, h_queries, qbytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess) return e;
+  if ((e = launch_search(p, sm_count, stream)) != cudaSuccess) return e;
+  if ((e = cudaMemcpyAsync(h_ids, p.out_ids, rbytes, cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return e;
+  if ((e = cudaMemcpyAsync(h_dist, p.out_dist, rbytes, cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return e;
+  if ((e = cudaMemcpyAsync(h_found, p.out_found, (size_t)nq * sizeof(int), cudaMemcpyDeviceToHost, stream)) !=
+      cudaSuccess)
+    return e;
+  return cudaStreamSynchronize(stream);
+}
+
+}  // namespace hnsw

@@ -32,6 +32,8 @@ SIGNATURES = {
                                        ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
   "cuhnsw_search_knn_device": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
                                               ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_search_knn_noalloc": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
+                                               ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
   "cuhnsw_batch_distance": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
                                             ctypes.c_void_p]),
   "cuhnsw_set_stream": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
@@ -139,6 +141,16 @@ class CuHNSWBind:
     """All arguments are device addresses (ints); enqueued, not waited for."""
     self._check(self._lib.cuhnsw_search_knn_device(self._h, q_ptr, nq, topk, ef_search, nns_ptr, dist_ptr,
                                                    found_ptr))
+
+  def search_knn_noalloc(self, qdata, topk, ef_search, nns, distances, found):
+    """search_knn for callers that cannot allocate device memory: device staging comes from a fixed
+    4 MiB array inside the library (see cuhnsw_search_knn_noalloc in include/cuhnsw_b200.h)."""
+    q = np.ascontiguousarray(qdata, dtype=np.float32)
+    if q.ndim not in (1, 2):
+      raise RuntimeError("data array must be 1d / 2d shape")
+    nq = 1 if q.ndim == 1 else q.shape[0]
+    self._check(self._lib.cuhnsw_search_knn_noalloc(self._h, q.ctypes.data, nq, topk, ef_search, nns.ctypes.data,
+                                                    distances.ctypes.data, found.ctypes.data))
 
   def batch_distance(self, src, dst):
     src = np.ascontiguousarray(src, np.int32)

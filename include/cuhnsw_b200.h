@@ -72,6 +72,24 @@ int cuhnsw_search_knn(cuhnsw_handle* h, const float* qdata, int64_t num_queries,
 int cuhnsw_search_knn_device(cuhnsw_handle* h, const float* d_qdata, int64_t num_queries, int32_t topk,
                              int32_t ef_search, int32_t* d_nns, float* d_distances, int32_t* d_found_cnt);
 
+/* Search for callers that must not allocate.  No counterpart in the reference (its SearchGraph allocates a dozen
+ * device vectors per call, cpp/src/cuhnsw_build.cu:241-249).  Same arguments and results as cuhnsw_search_knn (host
+ * buffers), but the call reaches no cudaMalloc/cudaFree or other allocating routine: the device copies of the
+ * queries and results and the kernel's work ticket live in one fixed 4 MiB array inside the library image, which
+ * every GPU that loads the library keeps until the process exits.  Meant for processes whose device memory is
+ * already owned by their own pool or capped by a budget (a late allocation would fail), and for loops that cannot
+ * take the device-wide synchronisation an allocation implies.
+ *  - Limit: 256 + 4*num_queries*num_dims + 8*num_queries*topk + 4*num_queries bytes (each term rounded up to
+ *    256) must not exceed 4 MiB, e.g. 10 000 queries of 50 dims at topk 10; larger requests fail with
+ *    CUHNSW_INVALID_ARGUMENT and a message that states both numbers.
+ *  - The first call on a device looks up the array's device address (a one-time set-up per device); make that
+ *    first call before any stream capture is started.
+ *  - The array is shared by all handles and calls of the process on that device and keeps the previous call's
+ *    contents; the call clears the one word that has to start at zero.  Calls that overlap on the GPU (two
+ *    threads, two streams) race on it: issue them one after the other. */
+int cuhnsw_search_knn_noalloc(cuhnsw_handle* h, const float* qdata, int64_t num_queries, int32_t topk,
+                              int32_t ef_search, int32_t* nns, float* distances, int32_t* found_cnt);
+
 /* out[i] = distance between stored rows src[i] and dst[i] (host arrays): squared l2 or -dot, in the engine's
  * fixed fp32 summation order.  Counterpart of BatchDistanceKernel (cpp/include/cuda_dist_kernels.cuh:143-156). */
 int cuhnsw_batch_distance(cuhnsw_handle* h, const int32_t* src, const int32_t* dst, int64_t num_pairs, float* out);

@@ -18,35 +18,58 @@
 
 namespace hnsw {
 
-struct WalkCounters {
-  unsigned long long evals;       // rows gathered for a distance
-  unsigned long long expansions;  // adjacency rows read at the searched layer
-  unsigned long long sweeps;      // adjacency rows read during greedy descent
-  unsigned long long inserts;     // keys merged into the list
+struct WalkCounters {  // per warp and launch
+  unsigned evals;       // rows gathered for a distance
+  unsigned expansions;  // adjacency rows read at the searched layer
+  unsigned sweeps;      // adjacency rows read during greedy descent
+  unsigned inserts;     // keys merged into the list
 };
+
+// Number of bits that hold every node id of an index with n nodes.
+__host__ __device__ inline int id_bits(long long n) {
+  int b = 1;
+  while (b < 31 && (1ll << b) < n) ++b;
+  return b;
+}
+// Bytes per visited-table entry: 2 when the tag that remains after the bucket number fits in 15 bits.
+__host__ __device__ inline int visited_entry_bytes(long long n, int entries) {
+  int kb = 0;
+  while ((2 << kb) < entries) ++kb;  // buckets = entries / 2 = 2^kb
+  int tag_bits = id_bits(n) - kb;
+  return tag_bits <= 15 ? 2 : 4;
+}
 
 // Per-warp shared-memory state.
 struct WarpList {
   unsigned long long* keys;  // ascending (distance, id); capacity `cap`
   int* spos;                 // 32 ints of scratch
-  unsigned* vt;              // visited table, vsize entries (power of two), 0xffffffff = empty
-  int vshift;                // 32 - log2(vsize)
-  int vsize;
+  unsigned* vt;              // visited table: buckets of two tags (2 x 16 bit in one word, or 2 x 32 bit)
+  unsigned hmask;            // 2^B - 1, B = id_bits(n)
+  int tag_bits;              // low bits of the hash kept as the tag; the rest is the bucket number
+  unsigned tag_mask;
+  bool wide;                 // 32-bit tags
+  int vbytes;
   int cap;
   int size;
   int cursor;  // every key before `cursor` is expanded
 
-  __host__ __device__ static constexpr size_t smem_bytes(int cap, int vsize) {
-    return (size_t)((cap + 31) / 32 * 32) * 8 + 32 * 4 + (size_t)vsize * 4;
+  __host__ __device__ static size_t smem_bytes(int cap, int entries, long long n) {
+    return (size_t)((cap + 31) / 32 * 32) * 8 + 32 * 4 + (size_t)entries * visited_entry_bytes(n, entries);
   }
-  __device__ __forceinline__ void bind(void* smem, int cap_, int vsize_) {
+  __device__ __forceinline__ void bind(void* smem, int cap_, int entries, long long n) {
     keys = reinterpret_cast<unsigned long long*>(smem);
     int capr = (cap_ + 31) / 32 * 32;
     spos = reinterpret_cast<int*>(keys + capr);
     vt = reinterpret_cast<unsigned*>(spos + 32);
     cap = cap_;
-    vsize = vsize_;
-    vshift = 32 - (31 - __clz(vsize_));
+    const int b = id_bits(n);
+    int kb = 0;
+    while ((2 << kb) < entries) ++kb;
+    tag_bits = b - kb > 0 ? b - kb : 0;
+    hmask = b >= 32 ? ~0u : ((1u << b) - 1u);
+    tag_mask = (1u << tag_bits) - 1u;
+    wide = tag_bits > 15;
+    vbytes = entries * (wide ? 4 : 2);
     size = 0;
     cursor = 0;
   }
@@ -56,23 +79,30 @@ struct WarpList {
   __device__ __forceinline__ void reset() {
     uint4* p = reinterpret_cast<uint4*>(vt);
     const uint4 e = make_uint4(~0u, ~0u, ~0u, ~0u);
-    for (int i = lane_id(); i < vsize / 4; i += 32) p[i] = e;
+    for (int i = lane_id(); i < vbytes / 16; i += 32) p[i] = e;
     size = 0;
     cursor = 0;
     __syncwarp();
   }
-  // Lossy set with no false positives: a hit means the id was recorded
-  // earlier; a miss records it (possibly displacing another id), which can
-  // only cause a repeated distance evaluation, never a different result,
-  // because duplicates are rejected when merging into the list.
+  // Lossy set with no false positives.  id -> h = id * odd mod 2^B is a bijection on B-bit
+  // numbers, so (bucket, tag) = (high bits, low bits) of h identifies the id exactly and only
+  // the tag has to be stored.  Each bucket keeps its two most recent tags; a displaced id can
+  // only cause a repeated distance evaluation, never a different result, because duplicates are
+  // rejected when merging into the list and a key that left the list can never re-enter.
   __device__ __forceinline__ bool test_and_set(int id) {
-    unsigned slot = ((unsigned)id * 2654435761u) >> vshift;
-    unsigned a = vt[slot];
-    if (a == (unsigned)id) return true;
-    unsigned b = vt[slot ^ 1];
-    if (b == (unsigned)id) return true;
-    if (a == ~0u || b != ~0u) vt[slot] = (unsigned)id;
-    else vt[slot ^ 1] = (unsigned)id;
+    const unsigned h = ((unsigned)id * 2654435761u) & hmask;
+    const unsigned bucket = h >> tag_bits;
+    const unsigned tag = h & tag_mask;
+    if (!wide) {
+      const unsigned w = vt[bucket];
+      if ((w & 0xffffu) == tag || (w >> 16) == tag) return true;
+      vt[bucket] = (w << 16) | tag;
+      return false;
+    }
+    uint2* p = reinterpret_cast<uint2*>(vt) + bucket;
+    const uint2 w = *p;
+    if (w.x == tag || w.y == tag) return true;
+    *p = make_uint2(tag, w.x);
     return false;
   }
   __device__ __forceinline__ void mark(int id) {
@@ -86,39 +116,66 @@ struct WarpList {
   // largest" (cuda_utils_kernels.cuh:220-225).
   __device__ __forceinline__ void merge(unsigned long long key, bool active, WalkCounters& wc) {
     const int lane = lane_id();
-    unsigned long long worst = (size >= cap) ? (keys[size - 1] & KEY_MASK) : KEY_MAX;
+    const unsigned long long worst = (size >= cap) ? (keys[size - 1] & KEY_MASK) : KEY_MAX;
     bool keep = active && key < worst;
-    if (!__any_sync(FULL, keep)) return;
-    // position = number of list keys smaller than the new key
-    int lo = 0, hi = keep ? size : 0;
-    while (__any_sync(FULL, lo < hi)) {
-      if (lo < hi) {
-        int mid = (lo + hi) >> 1;
-        if ((keys[mid] & KEY_MASK) < key) lo = mid + 1;
-        else hi = mid;
+    const unsigned km0 = __ballot_sync(FULL, keep);
+    if (km0 == 0) return;
+    // pos = number of list keys smaller than the new key
+    int pos = 0;
+    bool dup = false;
+    const int nch = (size + 31) >> 5;
+    if (__popc(km0) <= 6 && nch <= 32) {
+      // few newcomers: two-level search by the whole warp, one newcomer at a time
+      for (unsigned mm = km0; mm; mm &= mm - 1) {
+        const int b = __ffs(mm) - 1;
+        const unsigned long long kb = shfl64(key, b);
+        const unsigned long long pv = (lane < nch) ? (keys[min(lane * 32 + 31, size - 1)] & KEY_MASK) : KEY_MAX;
+        const int c = __popc(__ballot_sync(FULL, lane < nch && pv < kb));  // chunks entirely below kb
+        const int i = c * 32 + lane;
+        const unsigned long long kv = (c < nch && i < size) ? (keys[i] & KEY_MASK) : KEY_MAX;
+        const unsigned lt = __ballot_sync(FULL, kv < kb);
+        const unsigned eq = __ballot_sync(FULL, kv == kb);
+        if (lane == b) {
+          pos = c < nch ? c * 32 + __popc(lt) : size;
+          dup = eq != 0;
+        }
       }
+    } else {
+      int lo = 0, hi = keep ? size : 0;
+      while (__any_sync(FULL, lo < hi)) {
+        if (lo < hi) {
+          int mid = (lo + hi) >> 1;
+          if ((keys[mid] & KEY_MASK) < key) lo = mid + 1;
+          else hi = mid;
+        }
+      }
+      pos = lo;
+      dup = keep && pos < size && (keys[pos] & KEY_MASK) == key;
     }
-    const int pos = lo;
-    if (keep && pos < size && (keys[pos] & KEY_MASK) == key) keep = false;  // already listed
+    if (dup) keep = false;  // already listed
     const unsigned km = __ballot_sync(FULL, keep);
     if (km == 0) return;
     const int m = __popc(km);
     int rk = 0;
-    for (unsigned mm = km; mm; mm &= mm - 1) {
-      int b = __ffs(mm) - 1;
-      unsigned long long kb = shfl64(key, b);
-      rk += (kb < key) ? 1 : 0;
+    if (m > 1) {
+      for (unsigned mm = km; mm; mm &= mm - 1) {
+        const int b = __ffs(mm) - 1;
+        const unsigned long long kb = shfl64(key, b);
+        rk += (kb < key) ? 1 : 0;
+      }
+      if (keep) spos[rk] = pos;
+      __syncwarp();
     }
-    if (keep) spos[rk] = pos;
-    __syncwarp();
-    const int minpos = spos[0];
+    const int minpos = m > 1 ? spos[0] : __shfl_sync(FULL, pos, __ffs(km) - 1);
     for (int base = (size - 1) & ~31; size > 0 && base >= (minpos & ~31); base -= 32) {
-      int i = base + lane;
-      bool have = (i < size) && (i >= minpos);
-      unsigned long long v = have ? keys[i] : 0ull;
-      int cnt = 0;
-      if (have)
+      const int i = base + lane;
+      const bool have = (i < size) && (i >= minpos);
+      const unsigned long long v = have ? keys[i] : 0ull;
+      int cnt = 1;
+      if (m > 1 && have) {
+        cnt = 0;
         for (int j = 0; j < m; ++j) cnt += (spos[j] <= i) ? 1 : 0;
+      }
       __syncwarp();
       if (have && i + cnt < cap) keys[i + cnt] = v;
       __syncwarp();
@@ -148,52 +205,84 @@ struct WarpList {
   }
 };
 
-// Gathers one adjacency row chunk (32 ids per step), filters it through the
-// visited table, evaluates the fresh ids and merges them.  `rows` is a
-// sentinel-padded table: unused slots hold -1.
+// One chunk of an adjacency row (lane l holds the id in slot l, -1 = unused): filter through the
+// visited table, evaluate the fresh ids, merge them.
+template <class Dist>
+__device__ __forceinline__ void expand_chunk(Dist& de, WarpList& wl, int nid, int self, WalkCounters& wc) {
+  const int lane = lane_id();
+  bool fresh = (nid >= 0) && (nid != self);
+  if (fresh) fresh = !wl.test_and_set(nid);
+  const unsigned fm = __ballot_sync(FULL, fresh);
+  if (fm == 0) return;
+  const int n = __popc(fm);
+  if (fresh) wl.spos[__popc(fm & ((1u << lane) - 1))] = nid;
+  __syncwarp();
+  const int cid = wl.spos[lane];
+  __syncwarp();
+  const float dist = de.eval(cid, n);
+  wc.evals += n;
+  wl.merge(mkkey(dist, cid), lane < n, wc);
+}
+
+// Whole adjacency row; `rows` is a sentinel-padded table: unused slots hold -1.
 template <class Dist>
 __device__ __forceinline__ void expand_row(Dist& de, WarpList& wl, const int* __restrict__ row, int stride,
                                            int self, WalkCounters& wc) {
   const int lane = lane_id();
   for (int base = 0; base < stride; base += 32) {
-    int l = base + lane;
-    int nid = (l < stride) ? __ldg(row + l) : -1;
-    bool fresh = (nid >= 0) && (nid != self);
-    if (fresh) fresh = !wl.test_and_set(nid);
-    unsigned fm = __ballot_sync(FULL, fresh);
-    if (fm == 0) continue;
-    int n = __popc(fm);
-    if (fresh) wl.spos[__popc(fm & ((1u << lane) - 1))] = nid;
-    __syncwarp();
-    int cid = wl.spos[lane];
-    __syncwarp();
-    float dist = de.eval(cid, n);
-    wc.evals += n;
-    wl.merge(mkkey(dist, cid), lane < n, wc);
+    const int l = base + lane;
+    const int nid = (l < stride) ? __ldg(row + l) : -1;
+    expand_chunk(de, wl, nid, self, wc);
   }
 }
 
-// ef-bounded best-first search of one layer.  The list must already hold the
-// seeds; on return it holds the min(ef, reachable) closest nodes, ascending.
 // Row number of node `id` in the adjacency table of `level`: layer 0 is indexed by id,
 // the upper layers of a node are stored consecutively from upper_base[id].
 __device__ __forceinline__ size_t row_index(const int* __restrict__ upper_base, int level, int id) {
   return level == 0 ? (size_t)id : (size_t)__ldg(upper_base + id) + (size_t)(level - 1);
 }
 
+// ef-bounded best-first search of one layer.  The list must already hold the
+// seeds; on return it holds the min(ef, reachable) closest nodes, ascending.
+// While the neighbours of the current node are gathered, the first 32 slots of
+// the adjacency row of the likely next node (the key after the cursor) are
+// already on their way; a newcomer that overtakes it costs one ordinary load.
 template <class Dist>
 __device__ __forceinline__ void beam_layer(Dist& de, WarpList& wl, const int* __restrict__ rows, int stride,
                                            const int* __restrict__ upper_base, int level, int self,
                                            WalkCounters& wc) {
+  const int lane = lane_id();
+  int pf_node = -1, pf_val = -1;
   wl.advance();
   while (wl.cursor < wl.size) {
-    unsigned long long k = wl.keys[wl.cursor];
+    const unsigned long long k = wl.keys[wl.cursor];
+    const unsigned long long k2 = (wl.cursor + 1 < wl.size) ? wl.keys[wl.cursor + 1] : KEY_FLAG;
     __syncwarp();
-    if (lane_id() == 0) wl.keys[wl.cursor] = k | KEY_FLAG;
+    if (lane == 0) wl.keys[wl.cursor] = k | KEY_FLAG;
     __syncwarp();
     const int cur = key_id(k);
+    const int* row = rows + row_index(upper_base, level, cur) * stride;
+    int nid;
+    if (cur == pf_node) {
+      nid = pf_val;
+#ifdef HNSW_DEBUG_PF
+      wc.sweeps += 1;  // experiment: count prefetch hits in the sweeps slot
+#endif
+    } else {
+      nid = (lane < stride) ? __ldg(row + lane) : -1;
+    }
+    pf_node = -1;
+    if (!(k2 & KEY_FLAG)) {
+      pf_node = key_id(k2);
+      const int* nrow = rows + row_index(upper_base, level, pf_node) * stride;
+      pf_val = (lane < stride) ? __ldg(nrow + lane) : -1;
+    }
     wc.expansions += 1;
-    expand_row(de, wl, rows + row_index(upper_base, level, cur) * stride, stride, self, wc);
+    expand_chunk(de, wl, nid, self, wc);
+    for (int base = 32; base < stride; base += 32) {
+      const int l = base + lane;
+      expand_chunk(de, wl, (l < stride) ? __ldg(row + l) : -1, self, wc);
+    }
     wl.advance();
   }
 }

@@ -116,14 +116,14 @@ __device__ __forceinline__ void bind_warp(unsigned char* smem, int per_warp, con
   VecTable tab{reinterpret_cast<const float4*>(g.vec), g.vstride / 4, (g.d + 3) / 4, g.d, g.dist_type};
   de.init(tab, mine);
   mine += Dist::smem_bytes(g.d);
-  wl.bind(mine, cap, vsize);
-  mine += WarpList::smem_bytes(cap, vsize);
+  wl.bind(mine, cap, vsize, g.n);
+  mine += WarpList::smem_bytes(cap, vsize, g.n);
   sel.bind(mine);
 }
 
 template <class Dist>
-__host__ __device__ constexpr size_t build_smem_per_warp(int d, int cap, int vsize) {
-  return (Dist::smem_bytes(d) + WarpList::smem_bytes(cap, vsize) + SelBuf::smem_bytes() + 15) / 16 * 16;
+__host__ __device__ inline size_t build_smem_per_warp(int d, int cap, int vsize, long long n) {
+  return (Dist::smem_bytes(d) + WarpList::smem_bytes(cap, vsize, n) + SelBuf::smem_bytes() + 15) / 16 * 16;
 }
 
 // ---------------------------------------------------------------------------
@@ -207,7 +207,7 @@ struct BatchParams {
 };
 
 template <class Dist>
-__global__ void __launch_bounds__(kBuildWarps * 32) build_search_kernel(BatchParams p) {
+__global__ void __launch_bounds__(kBuildWarps * 32, Dist::kBuildMinCtas) build_search_kernel(BatchParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int lane = threadIdx.x & 31;
   const BuildLevel& L = p.L;
@@ -237,9 +237,9 @@ __global__ void __launch_bounds__(kBuildWarps * 32) build_search_kernel(BatchPar
     __syncwarp();
   }
   if (p.S.stats && lane == 0) {
-    atomicAdd(p.S.stats + 0, wc.evals);
-    atomicAdd(p.S.stats + 1, wc.expansions);
-    atomicAdd(p.S.stats + 3, wc.inserts);
+    atomicAdd(p.S.stats + 0, (unsigned long long)wc.evals);
+    atomicAdd(p.S.stats + 1, (unsigned long long)wc.expansions);
+    atomicAdd(p.S.stats + 3, (unsigned long long)wc.inserts);
   }
 }
 
@@ -267,7 +267,7 @@ __global__ void build_apply_kernel(BatchParams p) {
 // phase C: reverse links, one warp per target node
 // ---------------------------------------------------------------------------
 template <class Dist>
-__global__ void __launch_bounds__(kBuildWarps * 32) build_reverse_kernel(BatchParams p) {
+__global__ void __launch_bounds__(kBuildWarps * 32, Dist::kBuildMinCtas) build_reverse_kernel(BatchParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int lane = threadIdx.x & 31;
   const BuildLevel& L = p.L;
@@ -358,7 +358,7 @@ __global__ void __launch_bounds__(kBuildWarps * 32) build_reverse_kernel(BatchPa
       __syncwarp();
     }
   }
-  if (p.S.stats && lane == 0) atomicAdd(p.S.stats + 0, wc.evals);
+  if (p.S.stats && lane == 0) atomicAdd(p.S.stats + 0, (unsigned long long)wc.evals);
 }
 
 // ---------------------------------------------------------------------------
@@ -396,7 +396,7 @@ size_t build_sort_tmp_bytes(long long max_items) {
 template <class Dist>
 static cudaError_t init_level_t(const BuildLevel& L, unsigned long long* ticket, int sm_count, cudaStream_t stream) {
   InitParams p{L, 0, ticket};
-  size_t per_warp = build_smem_per_warp<Dist>(L.g.d, 32, 32);
+  size_t per_warp = build_smem_per_warp<Dist>(L.g.d, 32, 32, L.g.n);
   p.per_warp = (int)per_warp;
   size_t smem = per_warp * kBuildWarps;
   int grid = 1;
@@ -423,7 +423,7 @@ static cudaError_t build_batch_t(const BuildLevel& L, const BuildScratch& S, lon
   cudaError_t e = cudaMemsetAsync(S.ticket, 0, 2 * sizeof(unsigned long long), stream);
   if (e != cudaSuccess) return e;
   {
-    size_t per_warp = build_smem_per_warp<Dist>(L.g.d, p.cap, L.vsize);
+    size_t per_warp = build_smem_per_warp<Dist>(L.g.d, p.cap, L.vsize, L.g.n);
     p.per_warp = (int)per_warp;
     size_t smem = per_warp * kBuildWarps;
     int grid = 1;
@@ -447,7 +447,7 @@ static cudaError_t build_batch_t(const BuildLevel& L, const BuildScratch& S, lon
     if (e != cudaSuccess) return e;
   }
   {
-    size_t per_warp = build_smem_per_warp<Dist>(L.g.d, p.cap, 32);
+    size_t per_warp = build_smem_per_warp<Dist>(L.g.d, p.cap, 32, L.g.n);
     p.per_warp = (int)per_warp;
     size_t smem = per_warp * kBuildWarps;
     int grid = 1;

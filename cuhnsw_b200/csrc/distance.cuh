@@ -52,7 +52,22 @@ template <int C>
 struct DistSmall {
   static constexpr int kTeam = 8;
   static constexpr int kRowsPerPass = 4;
-  static constexpr int kBatch = (C <= 2) ? 6 : 4;  // passes whose loads are issued together
+  // Passes whose loads are issued together.  Measured on a B200: one pass per step and 64
+  // registers (32 resident warps per SM) beats deeper batches with fewer resident warps.
+#ifndef HNSW_DIST_BATCH
+#define HNSW_DIST_BATCH 1
+#endif
+  static constexpr int kBatch = HNSW_DIST_BATCH;
+  // resident CTAs (of 2 warps) per SM the walk kernels are compiled for
+#ifndef HNSW_SEARCH_MIN_CTAS
+#define HNSW_SEARCH_MIN_CTAS 16
+#endif
+#ifndef HNSW_BUILD_MIN_CTAS
+#define HNSW_BUILD_MIN_CTAS 12
+#endif
+  static constexpr int kSearchMinCtas = HNSW_SEARCH_MIN_CTAS;
+  static constexpr int kBuildMinCtas = HNSW_BUILD_MIN_CTAS;
+  static constexpr int kWarpsPerSmTarget = 32;
   __host__ __device__ static constexpr size_t smem_bytes(int) { return 0; }
 
   VecTable t;
@@ -129,6 +144,9 @@ struct DistSmall {
 struct DistLarge {
   static constexpr int kRows = 4;    // rows whose loads are in flight together
   static constexpr int kChunks = 4;  // chunk columns per row per step
+  static constexpr int kSearchMinCtas = 8;  // 16 float4 in flight per lane need ~125 registers
+  static constexpr int kBuildMinCtas = 8;
+  static constexpr int kWarpsPerSmTarget = 16;
   __host__ __device__ static constexpr size_t smem_bytes(int d) { return (size_t)((d + 127) / 128) * 128 * sizeof(float); }
 
   VecTable t;

@@ -264,10 +264,20 @@ GraphView Engine::View() const {
 
 int Engine::ResolveVsize(int cap, int* vsize) const {
   int v;
-  if (opt_.visited_table_size > 0) v = std::min(32768, std::max(64, next_pow2(opt_.visited_table_size)));
-  else v = std::min(4096, std::max(512, next_pow2(16ll * cap)));
-  while (v > 64 && search_smem_per_cta(d_, cap, v) + 4096 > smem_optin_) v >>= 1;
-  if (search_smem_per_cta(d_, cap, v) + 4096 > smem_optin_) return kUnsupported;
+  if (opt_.visited_table_size > 0) {
+    v = std::min(32768, std::max(64, next_pow2(opt_.visited_table_size)));
+  } else {
+    // Largest table that still lets the kernel keep its target number of warps resident per SM
+    // (the walk is latency bound: resident warps matter more than a few repeated evaluations),
+    // but never below ~4 entries per list slot, where repeats explode.
+    const int warps = d_ <= 128 ? 32 : 16;
+    const long long budget = (long long)smem_optin_ / warps - 640;
+    const int floor_entries = std::min(4096, std::max(512, next_pow2(4ll * cap)));
+    v = 4096;
+    while (v > floor_entries && (long long)search_smem_per_cta(d_, cap, v, n_) / 2 > budget) v >>= 1;
+  }
+  while (v > 64 && search_smem_per_cta(d_, cap, v, n_) + 4096 > smem_optin_) v >>= 1;
+  if (search_smem_per_cta(d_, cap, v, n_) + 4096 > smem_optin_) return kUnsupported;
   *vsize = v;
   return kOk;
 }

@@ -39,7 +39,7 @@ struct SearchParams {
 };
 
 cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream);
-size_t search_smem_per_cta(int d, int ef, int vsize);
+size_t search_smem_per_cta(int d, int ef, int vsize, long long n);
 // search whose device staging and work ticket live in a fixed file-scope device array (no allocation)
 size_t search_static_capacity();
 size_t search_static_bytes(long long nq, int d, int topk);

@@ -13,7 +13,7 @@ namespace hnsw {
 constexpr int kWarpsPerCta = 2;
 
 template <class Dist>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, Dist::kSearchMinCtas)
 knn_search_kernel(SearchParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -22,7 +22,7 @@ knn_search_kernel(SearchParams p) {
   VecTable tab{reinterpret_cast<const float4*>(p.g.vec), p.g.vstride / 4, (p.g.d + 3) / 4, p.g.d, p.g.dist_type};
   de.init(tab, mine);
   WarpList wl;
-  wl.bind(mine + Dist::smem_bytes(p.g.d), p.ef, p.vsize);
+  wl.bind(mine + Dist::smem_bytes(p.g.d), p.ef, p.vsize, p.g.n);
   WalkCounters wc{0, 0, 0, 0};
 
   for (;;) {
@@ -61,17 +61,17 @@ knn_search_kernel(SearchParams p) {
     __syncwarp();
   }
   if (p.stats && lane == 0) {
-    atomicAdd(p.stats + 0, wc.evals);
-    atomicAdd(p.stats + 1, wc.expansions);
-    atomicAdd(p.stats + 2, wc.sweeps);
-    atomicAdd(p.stats + 3, wc.inserts);
+    atomicAdd(p.stats + 0, (unsigned long long)wc.evals);
+    atomicAdd(p.stats + 1, (unsigned long long)wc.expansions);
+    atomicAdd(p.stats + 2, (unsigned long long)wc.sweeps);
+    atomicAdd(p.stats + 3, (unsigned long long)wc.inserts);
   }
 }
 
 template <class Dist>
 static cudaError_t launch_search_t(const SearchParams& p0, int sm_count, cudaStream_t stream) {
   SearchParams p = p0;
-  size_t per_warp = Dist::smem_bytes(p.g.d) + WarpList::smem_bytes(p.ef, p.vsize);
+  size_t per_warp = Dist::smem_bytes(p.g.d) + WarpList::smem_bytes(p.ef, p.vsize, p.g.n);
   per_warp = (per_warp + 15) / 16 * 16;
   p.smem_per_warp = (int)per_warp;
   size_t smem = per_warp * kWarpsPerCta;
@@ -92,9 +92,9 @@ static cudaError_t launch_search_t(const SearchParams& p0, int sm_count, cudaStr
   return cudaGetLastError();
 }
 
-size_t search_smem_per_cta(int d, int ef, int vsize) {
+size_t search_smem_per_cta(int d, int ef, int vsize, long long n) {
   size_t dq = d <= 128 ? 0 : DistLarge::smem_bytes(d);
-  size_t per_warp = (dq + WarpList::smem_bytes(ef, vsize) + 15) / 16 * 16;
+  size_t per_warp = (dq + WarpList::smem_bytes(ef, vsize, n) + 15) / 16 * 16;
   return per_warp * kWarpsPerCta;
 }
 

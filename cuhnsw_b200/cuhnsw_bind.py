@@ -12,7 +12,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libcuhnsw_b200.so")
+# CUHNSW_B200_LIB selects another build of the same library (kernel tuning experiments)
+LIB_PATH = os.environ.get("CUHNSW_B200_LIB") or os.path.join(_HERE, "libcuhnsw_b200.so")
 
 _f32p = ctypes.POINTER(ctypes.c_float)
 _i32p = ctypes.POINTER(ctypes.c_int32)

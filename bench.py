@@ -39,7 +39,7 @@ FLUSH_BYTES = 256 << 20  # > 126 MB L2
 def parse():
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
-  ap.add_argument("--steps", type=int, default=20)
+  ap.add_argument("--steps", type=int, default=50)
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--n", type=int, default=None, help="override base size (debugging only; invalid as a bench number)")
@@ -63,7 +63,7 @@ class ClockSampler:
     try:
       self.proc = subprocess.Popen(
         ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-         "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+         "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
       self.thread = threading.Thread(target=self._read, daemon=True)
       self.thread.start()
     except OSError:
@@ -287,7 +287,6 @@ def run_ours(args, rank, world, local_rank):
   value = total_q / (ms_dev * 1e-3)
   e2e = total_q / (ms_e2e * 1e-3)
   peak, peak_kind = measured_peak()
-  timed_q = nq * args.steps  # this rank's queries behind `stats`
   line = {
     "metric": "batch-search QPS at recall@10>=0.95", "value": value, "unit": "queries/s", "n_gpus": world,
     "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
@@ -304,8 +303,9 @@ def run_ours(args, rank, world, local_rank):
     "clocks": clocks,
   }
   # roofline of the search kernel (one launch per step)
-  counts = {"evals": stats["evals"] / timed_q, "expansions": stats["expansions"] / timed_q,
-            "sweeps": stats["sweeps"] / timed_q, "source": "device counters (repeat evaluations included)"}
+  counted_q = nq * (args.steps + args.warmup)  # the counters also saw the warm-up steps
+  counts = {"evals": stats["evals"] / counted_q, "expansions": stats["expansions"] / counted_q,
+            "sweeps": stats["sweeps"] / counted_q, "source": "device counters (repeat evaluations included)"}
   cpu = None
   if world == 1:
     try:

@@ -52,6 +52,7 @@ struct WarpList {
   int cap;
   int size;
   int cursor;  // every key before `cursor` is expanded
+  unsigned long long worst;  // largest key of a full list, KEY_MAX while there is room
 
   __host__ __device__ static size_t smem_bytes(int cap, int entries, long long n) {
     return (size_t)((cap + 31) / 32 * 32) * 8 + 32 * 4 + (size_t)entries * visited_entry_bytes(n, entries);
@@ -72,6 +73,7 @@ struct WarpList {
     vbytes = entries * (wide ? 4 : 2);
     size = 0;
     cursor = 0;
+    worst = KEY_MAX;
   }
   // The table size is proportional to the list capacity, so clearing it is
   // O(nodes touched); the reference resets through a touched-slot list
@@ -82,6 +84,7 @@ struct WarpList {
     for (int i = lane_id(); i < vbytes / 16; i += 32) p[i] = e;
     size = 0;
     cursor = 0;
+    worst = KEY_MAX;
     __syncwarp();
   }
   // Lossy set with no false positives.  id -> h = id * odd mod 2^B is a bijection on B-bit
@@ -113,13 +116,13 @@ struct WarpList {
   // Merges up to 32 new keys (one per lane, `active` lanes) into the list,
   // keeping the `cap` smallest.  Equivalent to inserting them one by one in any
   // order with "insert if not full or smaller than the largest, evicting the
-  // largest" (cuda_utils_kernels.cuh:220-225).
-  __device__ __forceinline__ void merge(unsigned long long key, bool active, WalkCounters& wc) {
+  // largest" (cuda_utils_kernels.cuh:220-225).  Returns the smallest position a
+  // newcomer took, or `cap` when nothing was inserted.
+  __device__ __forceinline__ int merge(unsigned long long key, bool active, WalkCounters& wc) {
     const int lane = lane_id();
-    const unsigned long long worst = (size >= cap) ? (keys[size - 1] & KEY_MASK) : KEY_MAX;
     bool keep = active && key < worst;
     const unsigned km0 = __ballot_sync(FULL, keep);
-    if (km0 == 0) return;
+    if (km0 == 0) return cap;
     // pos = number of list keys smaller than the new key
     int pos = 0;
     bool dup = false;
@@ -129,14 +132,17 @@ struct WarpList {
       for (unsigned mm = km0; mm; mm &= mm - 1) {
         const int b = __ffs(mm) - 1;
         const unsigned long long kb = shfl64(key, b);
-        const unsigned long long pv = (lane < nch) ? (keys[min(lane * 32 + 31, size - 1)] & KEY_MASK) : KEY_MAX;
-        const int c = __popc(__ballot_sync(FULL, lane < nch && pv < kb));  // chunks entirely below kb
+        int c = 0;
+        if (nch > 1) {
+          const unsigned long long pv = (lane < nch) ? (keys[min(lane * 32 + 31, size - 1)] & KEY_MASK) : KEY_MAX;
+          c = __popc(__ballot_sync(FULL, pv < kb));  // chunks entirely below kb (lanes >= nch hold KEY_MAX)
+        }
         const int i = c * 32 + lane;
-        const unsigned long long kv = (c < nch && i < size) ? (keys[i] & KEY_MASK) : KEY_MAX;
+        const unsigned long long kv = (i < size) ? (keys[i] & KEY_MASK) : KEY_MAX;
         const unsigned lt = __ballot_sync(FULL, kv < kb);
         const unsigned eq = __ballot_sync(FULL, kv == kb);
         if (lane == b) {
-          pos = c < nch ? c * 32 + __popc(lt) : size;
+          pos = min(c * 32 + __popc(lt), size);
           dup = eq != 0;
         }
       }
@@ -154,10 +160,22 @@ struct WarpList {
     }
     if (dup) keep = false;  // already listed
     const unsigned km = __ballot_sync(FULL, keep);
-    if (km == 0) return;
+    if (km == 0) return cap;
     const int m = __popc(km);
-    int rk = 0;
-    if (m > 1) {
+    int minpos;
+    if (m == 1) {
+      // the common case: one newcomer, everything from its position on moves up by one
+      minpos = __shfl_sync(FULL, pos, __ffs(km) - 1);
+      for (int base = (size - 1) & ~31; size > 0 && base >= (minpos & ~31); base -= 32) {
+        const int i = base + lane;
+        const bool have = (i < size) && (i >= minpos);
+        const unsigned long long v = have ? keys[i] : 0ull;
+        __syncwarp();
+        if (have && i + 1 < cap) keys[i + 1] = v;
+      }
+      if (keep) keys[pos] = key;  // pos < cap: either the list is not full or key < worst
+    } else {
+      int rk = 0;
       for (unsigned mm = km; mm; mm &= mm - 1) {
         const int b = __ffs(mm) - 1;
         const unsigned long long kb = shfl64(key, b);
@@ -165,25 +183,33 @@ struct WarpList {
       }
       if (keep) spos[rk] = pos;
       __syncwarp();
-    }
-    const int minpos = m > 1 ? spos[0] : __shfl_sync(FULL, pos, __ffs(km) - 1);
-    for (int base = (size - 1) & ~31; size > 0 && base >= (minpos & ~31); base -= 32) {
-      const int i = base + lane;
-      const bool have = (i < size) && (i >= minpos);
-      const unsigned long long v = have ? keys[i] : 0ull;
-      int cnt = 1;
-      if (m > 1 && have) {
-        cnt = 0;
-        for (int j = 0; j < m; ++j) cnt += (spos[j] <= i) ? 1 : 0;
+      minpos = spos[0];
+      for (int base = (size - 1) & ~31; size > 0 && base >= (minpos & ~31); base -= 32) {
+        const int i = base + lane;
+        const bool have = (i < size) && (i >= minpos);
+        const unsigned long long v = have ? keys[i] : 0ull;
+        int cnt = 0;
+        if (have)
+          for (int j = 0; j < m; ++j) cnt += (spos[j] <= i) ? 1 : 0;
+        __syncwarp();
+        if (have && i + cnt < cap) keys[i + cnt] = v;
       }
-      __syncwarp();
-      if (have && i + cnt < cap) keys[i + cnt] = v;
-      __syncwarp();
+      if (keep && pos + rk < cap) keys[pos + rk] = key;
     }
-    if (keep && pos + rk < cap) keys[pos + rk] = key;
     size = min(cap, size + m);
     cursor = min(cursor, minpos);
     wc.inserts += m;
+    __syncwarp();
+    worst = (size >= cap) ? (keys[cap - 1] & KEY_MASK) : KEY_MAX;
+    return minpos;
+  }
+
+  // list = {key}
+  __device__ __forceinline__ void seed(unsigned long long key) {
+    if (lane_id() == 0) keys[0] = key;
+    size = 1;
+    cursor = 0;
+    worst = cap <= 1 ? (key & KEY_MASK) : KEY_MAX;
     __syncwarp();
   }
 
@@ -208,20 +234,20 @@ struct WarpList {
 // One chunk of an adjacency row (lane l holds the id in slot l, -1 = unused): filter through the
 // visited table, evaluate the fresh ids, merge them.
 template <class Dist>
-__device__ __forceinline__ void expand_chunk(Dist& de, WarpList& wl, int nid, int self, WalkCounters& wc) {
+__device__ __forceinline__ int expand_chunk(Dist& de, WarpList& wl, int nid, int self, WalkCounters& wc) {
   const int lane = lane_id();
   bool fresh = (nid >= 0) && (nid != self);
   if (fresh) fresh = !wl.test_and_set(nid);
   const unsigned fm = __ballot_sync(FULL, fresh);
-  if (fm == 0) return;
+  if (fm == 0) return wl.cap;
   const int n = __popc(fm);
   if (fresh) wl.spos[__popc(fm & ((1u << lane) - 1))] = nid;
   __syncwarp();
   const int cid = wl.spos[lane];
-  __syncwarp();
+  // the shuffles inside eval() order this read before any later write of spos
   const float dist = de.eval(cid, n);
   wc.evals += n;
-  wl.merge(mkkey(dist, cid), lane < n, wc);
+  return wl.merge(mkkey(dist, cid), lane < n, wc);
 }
 
 // Whole adjacency row; `rows` is a sentinel-padded table: unused slots hold -1.
@@ -254,10 +280,11 @@ __device__ __forceinline__ void beam_layer(Dist& de, WarpList& wl, const int* __
   const int lane = lane_id();
   int pf_node = -1, pf_val = -1;
   wl.advance();
-  while (wl.cursor < wl.size) {
-    const unsigned long long k = wl.keys[wl.cursor];
+  if (wl.cursor >= wl.size) return;
+  unsigned long long k = wl.keys[wl.cursor];
+  for (;;) {
+    // k = keys[cursor] is the closest unexpanded key
     const unsigned long long k2 = (wl.cursor + 1 < wl.size) ? wl.keys[wl.cursor + 1] : KEY_FLAG;
-    __syncwarp();
     if (lane == 0) wl.keys[wl.cursor] = k | KEY_FLAG;
     __syncwarp();
     const int cur = key_id(k);
@@ -278,12 +305,24 @@ __device__ __forceinline__ void beam_layer(Dist& de, WarpList& wl, const int* __
       pf_val = (lane < stride) ? __ldg(nrow + lane) : -1;
     }
     wc.expansions += 1;
-    expand_chunk(de, wl, nid, self, wc);
+    const int at = wl.cursor;  // position of the key being expanded; insertions at or before it move the cursor
+    int first_new = expand_chunk(de, wl, nid, self, wc);
     for (int base = 32; base < stride; base += 32) {
       const int l = base + lane;
-      expand_chunk(de, wl, (l < stride) ? __ldg(row + l) : -1, self, wc);
+      first_new = min(first_new, expand_chunk(de, wl, (l < stride) ? __ldg(row + l) : -1, self, wc));
     }
+    // next key: a newcomer placed at or before at + 1, else the old successor if it is still unexpanded,
+    // else scan on
+    if (first_new > at + 1 && !(k2 & KEY_FLAG)) {
+      // no newcomer in front of the old successor: it sits at at + 1 unchanged
+      wl.cursor = at + 1;
+      k = k2;
+      continue;
+    }
+    __syncwarp();
     wl.advance();
+    if (wl.cursor >= wl.size) break;
+    k = wl.keys[wl.cursor];
   }
 }
 

@@ -38,9 +38,7 @@ knn_search_kernel(SearchParams p) {
     wc.evals += 1;
     greedy_descent(de, wl.spos, p.g.rowsU, p.g.strideU, p.g.upper_base, p.g.max_level, 0, cur, dcur, wc);
     // layer 0: list = {entry}, visited = {entry} (cuda_search_kernels.cuh:108-112)
-    if (lane == 0) wl.keys[0] = mkkey(dcur, cur);
-    wl.size = 1;
-    wl.cursor = 0;
+    wl.seed(mkkey(dcur, cur));
     wl.mark(cur);
     beam_layer(de, wl, p.g.rows0, p.g.stride0, p.g.upper_base, 0, -1, wc);
     // ascending top-k, found = min(size, k); slots past `found` read -1 / +inf

@@ -326,6 +326,42 @@ __device__ __forceinline__ void beam_layer(Dist& de, WarpList& wl, const int* __
   }
 }
 
+// reverse_cand variant (cuda_utils_kernels.cuh:113-124 of the reference): every step expands
+// the FARTHEST unexpanded key of the list; the walk ends when every key is expanded.
+template <class Dist>
+__device__ __forceinline__ void beam_layer_reverse(Dist& de, WarpList& wl, const int* __restrict__ rows, int stride,
+                                                   const int* __restrict__ upper_base, int level, int self,
+                                                   WalkCounters& wc) {
+  const int lane = lane_id();
+  int hi = wl.size - 1;  // every key above `hi` is expanded
+  for (;;) {
+    int at = -1;
+    for (int base = hi & ~31; hi >= 0 && base >= 0; base -= 32) {
+      const int i = base + lane;
+      const bool open = (i <= hi) && !(wl.keys[i] & KEY_FLAG);
+      const unsigned m = __ballot_sync(FULL, open);
+      if (m) {
+        at = base + 31 - __clz(m);
+        break;
+      }
+    }
+    if (at < 0) break;
+    const unsigned long long k = wl.keys[at];
+    __syncwarp();
+    if (lane == 0) wl.keys[at] = k | KEY_FLAG;
+    __syncwarp();
+    const int* row = rows + row_index(upper_base, level, key_id(k)) * stride;
+    wc.expansions += 1;
+    int first_new = wl.cap;
+    for (int base = 0; base < stride; base += 32) {
+      const int l = base + lane;
+      first_new = min(first_new, expand_chunk(de, wl, (l < stride) ? __ldg(row + l) : -1, self, wc));
+    }
+    __syncwarp();
+    hi = (first_new < wl.cap) ? wl.size - 1 : at - 1;
+  }
+}
+
 // Greedy walk through layers top..bottom+1: in each layer, evaluate every
 // neighbour of the current node, move to the closest one if it is strictly
 // closer (first in row order among equals), repeat until no move.

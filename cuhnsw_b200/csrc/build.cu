@@ -226,7 +226,8 @@ __global__ void __launch_bounds__(kBuildWarps * 32, Dist::kBuildMinCtas) build_s
     wl.reset();
     // seeds: the node's current row (cuda_build_kernels.cuh:203-212)
     expand_row(de, wl, L.rows + row_index(L.g.upper_base, L.level, s) * L.stride, L.stride, s, wc);
-    beam_layer(de, wl, L.rows, L.stride, L.g.upper_base, L.level, s, wc);
+    if (L.reverse_cand) beam_layer_reverse(de, wl, L.rows, L.stride, L.g.upper_base, L.level, s, wc);
+    else beam_layer(de, wl, L.rows, L.stride, L.g.upper_base, L.level, s, wc);
     int deg = select_neighbors(de, wl.keys, wl.size, L.max_m, p.nn_num, L.save_remains, -1, sel, wc);
     int* so = p.S.st_ids + (size_t)t * L.stride;
     float* sd = p.S.st_dist + (size_t)t * L.stride;

@@ -142,8 +142,6 @@ int Engine::Init(const char* opt_path) {
   if (o.heuristic_coef < 0.0 || o.heuristic_coef > 1.0)
     return Fail(kInvalidOption, "need 0 <= heuristic_coef <= 1");
   if (o.block_dim < 32 || o.block_dim > 1024 || o.block_dim % 32) return Fail(kInvalidOption, "invalid block_dim");
-  if (o.reverse_cand)
-    return Fail(kUnsupported, "reverse_cand=true (expand the farthest candidate first) is not implemented");
   if (o.ramp_div < 1) o.ramp_div = 1;
   opt_ = o;
   inited_ = true;
@@ -366,6 +364,7 @@ int Engine::BuildGraph() {
     L.ef_construction = opt_.ef_construction;
     L.heuristic_coef = (float)opt_.heuristic_coef;
     L.save_remains = opt_.save_remains ? 1 : 0;
+    L.reverse_cand = opt_.reverse_cand ? 1 : 0;
     L.vsize = vsize;
     CU(launch_init_level(L, counters_.get() + 3, sm_count_, stream_));
     long long p = 0;
@@ -412,6 +411,7 @@ int Engine::SearchGraphDevice(const float* d_q, long long nq, int topk, int ef, 
   p.topk = topk;
   p.ef = ef;
   p.vsize = vsize;
+  p.reverse_cand = opt_.reverse_cand ? 1 : 0;
   p.smem_per_warp = 0;
   p.labels = labelled_ ? labels_d_.get() : nullptr;
   p.out_ids = d_nns;
@@ -477,6 +477,7 @@ int Engine::SearchGraphStatic(const float* q, long long nq, int topk, int ef, in
   p.topk = topk;
   p.ef = ef;
   p.vsize = vsize;
+  p.reverse_cand = opt_.reverse_cand ? 1 : 0;
   p.smem_per_warp = 0;
   p.labels = labelled_ ? labels_d_.get() : nullptr;
   p.out_ids = nullptr;

@@ -29,6 +29,7 @@ struct SearchParams {
   int topk;
   int ef;
   int vsize;             // visited table entries per warp (power of two)
+  int reverse_cand;      // expand the farthest unexpanded key first
   int smem_per_warp;     // filled by the launcher
   const int* labels;     // optional id -> label map (index loaded from a file)
   int* out_ids;          // nq x topk
@@ -62,6 +63,7 @@ struct BuildLevel {
   int ef_construction;
   float heuristic_coef;
   int save_remains;
+  int reverse_cand;
   int vsize;
 };
 

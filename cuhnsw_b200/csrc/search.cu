@@ -12,7 +12,7 @@ namespace hnsw {
 
 constexpr int kWarpsPerCta = 2;
 
-template <class Dist>
+template <class Dist, bool kReverse>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, Dist::kSearchMinCtas)
 knn_search_kernel(SearchParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
@@ -40,7 +40,8 @@ knn_search_kernel(SearchParams p) {
     // layer 0: list = {entry}, visited = {entry} (cuda_search_kernels.cuh:108-112)
     wl.seed(mkkey(dcur, cur));
     wl.mark(cur);
-    beam_layer(de, wl, p.g.rows0, p.g.stride0, p.g.upper_base, 0, -1, wc);
+    if (kReverse) beam_layer_reverse(de, wl, p.g.rows0, p.g.stride0, p.g.upper_base, 0, -1, wc);
+    else beam_layer(de, wl, p.g.rows0, p.g.stride0, p.g.upper_base, 0, -1, wc);
     // ascending top-k, found = min(size, k); slots past `found` read -1 / +inf
     int found = min(wl.size, p.topk);
     for (int j = lane; j < p.topk; j += 32) {
@@ -66,14 +67,23 @@ knn_search_kernel(SearchParams p) {
   }
 }
 
+template <class Dist, bool kReverse>
+static cudaError_t launch_search_tr(const SearchParams& p0, int sm_count, cudaStream_t stream);
+
 template <class Dist>
 static cudaError_t launch_search_t(const SearchParams& p0, int sm_count, cudaStream_t stream) {
+  return p0.reverse_cand ? launch_search_tr<Dist, true>(p0, sm_count, stream)
+                         : launch_search_tr<Dist, false>(p0, sm_count, stream);
+}
+
+template <class Dist, bool kReverse>
+static cudaError_t launch_search_tr(const SearchParams& p0, int sm_count, cudaStream_t stream) {
   SearchParams p = p0;
   size_t per_warp = Dist::smem_bytes(p.g.d) + WarpList::smem_bytes(p.ef, p.vsize, p.g.n);
   per_warp = (per_warp + 15) / 16 * 16;
   p.smem_per_warp = (int)per_warp;
   size_t smem = per_warp * kWarpsPerCta;
-  auto kern = knn_search_kernel<Dist>;
+  auto kern = knn_search_kernel<Dist, kReverse>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   int per_sm = 0;

@@ -54,12 +54,12 @@ def _load(native=False):
   lib.oracle_search.argtypes = [
     ctypes.c_int64, ctypes.c_int, ctypes.c_int, f32p, ctypes.c_int, ctypes.c_int, i32p, i32p, i32p, i32p, i32p,
     ctypes.c_int, ctypes.c_int, f32p, ctypes.c_int64, ctypes.c_int, ctypes.c_int, i32p, f32p, i32p,
-    ctypes.c_void_p, ctypes.c_int]
+    ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
   lib.oracle_build.restype = ctypes.c_int
   lib.oracle_build.argtypes = [
     ctypes.c_int64, ctypes.c_int, ctypes.c_int, f32p, i32p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
     ctypes.c_double, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, i32p, i32p, f32p, i32p, i32p, i32p, f32p,
-    ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int), ctypes.c_void_p, ctypes.c_int]
+    ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int), ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
   lib.oracle_bruteforce.restype = ctypes.c_int
   lib.oracle_bruteforce.argtypes = [
     ctypes.c_int64, ctypes.c_int, ctypes.c_int, f32p, f32p, ctypes.c_int64, ctypes.c_int, i32p, f32p, ctypes.c_int]
@@ -104,7 +104,7 @@ class Graph:
 
 
 def build_graph(vec, levels, max_m, max_m0, dist_type, ef_construction, heuristic_coef=0.25, save_remains=False,
-                bmax=1, ramp_div=16, nthreads=0, native=False):
+                bmax=1, ramp_div=16, nthreads=0, native=False, reverse_cand=False):
   """Oracle build.  ``bmax=1`` is the strictly sequential reference-semantics
   schedule; any other value mirrors the batch schedule of the CUDA build."""
   g = Graph(vec, levels, max_m, max_m0, dist_type)
@@ -113,7 +113,7 @@ def build_graph(vec, levels, max_m, max_m0, dist_type, ef_construction, heuristi
   rc = _load(native).oracle_build(
     g.n, g.d, DIST[dist_type], g.vec, g.levels, g.max_m, g.max_m0, int(ef_construction), float(heuristic_coef),
     int(bool(save_remains)), int(bmax), int(ramp_div), g.rows0, g.deg0, g.dist0, g.upper_base, g.rowsU, g.degU,
-    g.distU, ctypes.byref(ml), ctypes.byref(ep), counters.ctypes.data, int(nthreads))
+    g.distU, ctypes.byref(ml), ctypes.byref(ep), counters.ctypes.data, int(nthreads), int(bool(reverse_cand)))
   assert rc == 0
   g.max_level, g.enter_point = ml.value, ep.value
   g.build_counters = counters
@@ -124,7 +124,7 @@ def build_graph(vec, levels, max_m, max_m0, dist_type, ef_construction, heuristi
   return g
 
 
-def search(g, queries, topk, ef, counters=False, nthreads=0, native=False):
+def search(g, queries, topk, ef, counters=False, nthreads=0, native=False, reverse_cand=False):
   q = np.ascontiguousarray(queries, np.float32)
   if q.ndim == 1:
     q = q[None, :]
@@ -136,7 +136,7 @@ def search(g, queries, topk, ef, counters=False, nthreads=0, native=False):
   rc = _load(native).oracle_search(
     g.n, g.d, DIST[g.dist_type], g.vec, g.max_m, g.max_m0, g.rows0, g.deg0, g.upper_base, g.rowsU, g.degU,
     g.max_level, g.enter_point, q, nq, int(topk), int(ef), ids, dist, found,
-    cnt.ctypes.data if counters else None, int(nthreads))
+    cnt.ctypes.data if counters else None, int(nthreads), int(bool(reverse_cand)))
   assert rc == 0
   if g.labels is not None:
     valid = ids >= 0

@@ -190,6 +190,7 @@ typedef struct {
   int *degU;            /* total_upper                                     */
   float *distU;         /* total_upper x max_m (build only)                */
   int max_level, enter_point;
+  int reverse_cand;     /* expand the farthest unexpanded key first (cuda_utils_kernels.cuh:113-124) */
 } graph_t;
 
 static inline int level_stride(const graph_t *g, int l) { return l ? g->max_m : g->max_m0; }
@@ -262,6 +263,16 @@ static int greedy_level(const graph_t *g, const float *q, int cur, float *dcur, 
   return cur;
 }
 
+/* copies a max-heap into an ascending array without keeping the heap; returns count */
+static int drain_sorted_keep(uint64_t *heap, int n, uint64_t *out) {
+  int total = n;
+  while (n > 0) {
+    int pos = n - 1;
+    out[pos] = maxheap_pop(heap, &n);
+  }
+  return total;
+}
+
 /* ef-bounded best-first search in one layer.  `res` holds the result set as a
  * max-heap of at most ef keys; a node enters iff the set is not full or its
  * key is smaller than the largest key; expansion always takes the smallest
@@ -269,8 +280,50 @@ static int greedy_level(const graph_t *g, const float *q, int cur, float *dcur, 
  * full result set (cuda_search_kernels.cuh:114-139,
  * cuda_utils_kernels.cuh:220-225).  Seeds must already be in cand/res/visited.
  * `self` (>= 0) is never inserted (build: cuda_utils_kernels.cuh:157). */
+#define ORACLE_FLAG 0x80000000ull
+/* reverse_cand variant: the result set is a sorted array with an "expanded" flag per key (bit 31 of the
+ * id word, masked in comparisons); every step expands the LARGEST unexpanded key and the walk ends when
+ * every key of the set is expanded.  Uses sc->cand as the array; leaves sc->res a valid max-heap. */
+static void beam_layer_reverse(const graph_t *g, const float *q, int l, int ef, scratch_t *sc, int *nres, int self,
+                               int64_t *evals, int64_t *expansions) {
+  uint64_t *w = sc->cand;
+  int n = drain_sorted_keep(sc->res, *nres, w);
+  for (;;) {
+    int at = n - 1;
+    while (at >= 0 && (w[at] & ORACLE_FLAG)) --at;
+    if (at < 0) break;
+    int c = (int)((uint32_t)w[at] & 0x7fffffffu);
+    w[at] |= ORACLE_FLAG;
+    const int *row = row_ids(g, c, l);
+    int deg = *row_deg(g, c, l);
+    if (expansions) (*expansions)++;
+    for (int j = 0; j < deg; ++j) {
+      int nb = row[j];
+      if (nb == self || sc->stamp[nb] == sc->epoch) continue;
+      sc->stamp[nb] = sc->epoch;
+      uint64_t k = mkkey(gdist(g, q, nb), nb);
+      if (evals) (*evals)++;
+      if (n >= ef) {
+        if (!(k < (w[n - 1] & ~ORACLE_FLAG))) continue;
+        --n; /* evict the largest key */
+      }
+      int pos = n;
+      while (pos > 0 && (w[pos - 1] & ~ORACLE_FLAG) > k) { w[pos] = w[pos - 1]; --pos; }
+      w[pos] = k;
+      ++n;
+    }
+  }
+  *nres = 0;
+  for (int i = 0; i < n; ++i) maxheap_push(sc->res, nres, w[i] & ~ORACLE_FLAG);
+}
+
 static void beam_layer(const graph_t *g, const float *q, int l, int ef, scratch_t *sc, int *ncand, int *nres,
                        int self, int64_t *evals, int64_t *expansions) {
+  if (g->reverse_cand) {
+    beam_layer_reverse(g, q, l, ef, sc, nres, self, evals, expansions);
+    *ncand = 0;
+    return;
+  }
   while (*ncand > 0) {
     uint64_t ck = sc->cand[0];
     if (*nres >= ef && ck > sc->res[0]) break;
@@ -318,13 +371,14 @@ static int drain_sorted(uint64_t *heap, int n, uint64_t *out) {
 int oracle_search(int64_t n, int d, int dist_type, const float *vec, int max_m, int max_m0, const int *rows0,
                   const int *deg0, const int *upper_base, const int *rowsU, const int *degU, int max_level,
                   int enter_point, const float *queries, int64_t nq, int topk, int ef, int *out_ids,
-                  float *out_dist, int *out_found, int64_t *counters, int nthreads) {
+                  float *out_dist, int *out_found, int64_t *counters, int nthreads, int reverse_cand) {
   if (ef < topk) ef = topk;
   graph_t g;
   memset(&g, 0, sizeof(g));
   g.n = n; g.d = d; g.dist_type = dist_type; g.max_m = max_m; g.max_m0 = max_m0;
   g.vec = vec; g.rows0 = (int *)rows0; g.deg0 = (int *)deg0; g.upper_base = upper_base;
   g.rowsU = (int *)rowsU; g.degU = (int *)degU; g.max_level = max_level; g.enter_point = enter_point;
+  g.reverse_cand = reverse_cand;
   if (n <= 0) {
     for (int64_t i = 0; i < nq; ++i) out_found[i] = 0;
     return 0;
@@ -460,12 +514,14 @@ static int64_t next_batch(int64_t reachable, int64_t left, int64_t bmax, int64_t
 int oracle_build(int64_t n, int d, int dist_type, const float *vec, const int *levels, int max_m, int max_m0,
                  int ef_construction, double heuristic_coef, int save_remains, int64_t bmax, int64_t ramp_div,
                  int *rows0, int *deg0, float *dist0, const int *upper_base, int *rowsU, int *degU,
-                 float *distU, int *out_max_level, int *out_enter_point, int64_t *build_counters, int nthreads) {
+                 float *distU, int *out_max_level, int *out_enter_point, int64_t *build_counters, int nthreads,
+                 int reverse_cand) {
   graph_t g;
   memset(&g, 0, sizeof(g));
   g.n = n; g.d = d; g.dist_type = dist_type; g.max_m = max_m; g.max_m0 = max_m0;
   g.vec = vec; g.rows0 = rows0; g.deg0 = deg0; g.dist0 = dist0; g.upper_base = upper_base;
   g.rowsU = rowsU; g.degU = degU; g.distU = distU;
+  g.reverse_cand = reverse_cand;
   /* first node that reaches the maximum level (cuhnsw_base.cu:134-141) */
   int max_level = 0, enter = 0;
   for (int64_t i = 0; i < n; ++i)

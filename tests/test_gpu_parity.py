@@ -153,6 +153,29 @@ def test_user_visited_table_size_does_not_change_results(tmp_path):
     assert (eng.search_knn(q, 10, 300)[0] == want).all()
 
 
+def test_reverse_cand_search_and_build_bit_exact(tmp_path):
+  """reverse_cand=True expands the farthest unexpanded candidate first, in search and in build
+  (cuda_utils_kernels.cuh:113-124, cuhnsw_build.cu:176,270)."""
+  base, q, opt = small_workload("angular_toy", 6000, 200)
+  eng = CuHNSW(engine_options(opt, reverse_cand=True, batch_max=400))
+  eng.set_data(base)
+  eng.build()
+  levels, rows0, rows_u = eng.obj.get_graph()
+  g = oracle.build_graph(base, levels, 12, 24, "dot", 110, bmax=400, reverse_cand=True)
+  assert (rows0 == g.rows0).all() and (rows_u[:g.rowsU.shape[0]] == g.rowsU).all()
+  for ef in (10, 64, 200):
+    ids, dist, found = eng.search_knn(q, 10, ef)
+    oids, odist, ofound = oracle.search(g, q, 10, ef, reverse_cand=True)
+    assert (ids == oids).all() and (found == ofound).all()
+    assert_same_bits(dist, odist)
+  # the forward search on the same graph is a different walk
+  fwd = CuHNSW(engine_options(opt))
+  path = str(tmp_path / "r.index")
+  eng.save_index(path)
+  fwd.load_index(path)
+  assert (fwd.search_knn(q, 10, 64)[0] == oracle.search(g, q, 10, 64)[0]).all()
+
+
 # ---------------------------------------------------------------- build
 BUILD_CASES = [  # workload, n, heuristic_coef, save_remains, batch_max
   ("angular_toy", 20000, 0.25, False, 0),

@@ -61,8 +61,9 @@ def test_init_error_behaviour_matches_reference_binding():
       b.init(write_opt(tmp, {"dist_type": "hamming"}))
     with pytest.raises(RuntimeError, match="max_m"):
       b.init(write_opt(tmp, {"max_m": 40, "max_m0": 24}))
-    with pytest.raises(RuntimeError, match="reverse_cand"):
-      b.init(write_opt(tmp, {"reverse_cand": True}))
+    with pytest.raises(RuntimeError, match="heuristic_coef"):
+      b.init(write_opt(tmp, {"heuristic_coef": 1.5}))
+    assert b.init(write_opt(tmp, {"reverse_cand": True})) is True
     assert b.init(write_opt(tmp, {"dist_type": "l2", "heuristic_coff": 0.5, "unknown_key": 3})) is True
     assert b.init(write_opt(tmp, "{}")) is True
 

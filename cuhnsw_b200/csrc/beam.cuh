@@ -127,7 +127,7 @@ struct WarpList {
     int pos = 0;
     bool dup = false;
     const int nch = (size + 31) >> 5;
-    if (__popc(km0) <= 6 && nch <= 32) {
+    if (__popc(km0) <= 2 && nch <= 32) {
       // few newcomers: two-level search by the whole warp, one newcomer at a time
       for (unsigned mm = km0; mm; mm &= mm - 1) {
         const int b = __ffs(mm) - 1;
@@ -166,9 +166,9 @@ struct WarpList {
     if (m == 1) {
       // the common case: one newcomer, everything from its position on moves up by one
       minpos = __shfl_sync(FULL, pos, __ffs(km) - 1);
-      for (int base = (size - 1) & ~31; size > 0 && base >= (minpos & ~31); base -= 32) {
-        const int i = base + lane;
-        const bool have = (i < size) && (i >= minpos);
+      for (int hi = size; hi > minpos; hi -= 32) {  // windows [hi - 32, hi), top down
+        const int i = hi - 32 + lane;
+        const bool have = i >= minpos;
         const unsigned long long v = have ? keys[i] : 0ull;
         __syncwarp();
         if (have && i + 1 < cap) keys[i + 1] = v;
@@ -184,9 +184,9 @@ struct WarpList {
       if (keep) spos[rk] = pos;
       __syncwarp();
       minpos = spos[0];
-      for (int base = (size - 1) & ~31; size > 0 && base >= (minpos & ~31); base -= 32) {
-        const int i = base + lane;
-        const bool have = (i < size) && (i >= minpos);
+      for (int hi = size; hi > minpos; hi -= 32) {
+        const int i = hi - 32 + lane;
+        const bool have = i >= minpos;
         const unsigned long long v = have ? keys[i] : 0ull;
         int cnt = 0;
         if (have)

@@ -98,39 +98,44 @@ struct DistSmall {
     }
   }
 
-  // Lane r (r < n <= 32) holds a row id; returns the distance to it in lane r.
+  // Lane r (r < n <= 32, n >= 1) holds a row id; returns the distance to it in lane r.
   __device__ __forceinline__ float eval(int id, int n) {
+    return t.dist_type == DIST_DOT ? eval_t<true>(id, n) : eval_t<false>(id, n);
+  }
+
+  template <bool kDot>
+  __device__ __forceinline__ float eval_t(int id, int n) {
     const int lane = lane_id();
     const int team = lane >> 3, tl = lane & 7;
-    const int npass = (n + 3) >> 2;
     float result = 0.0f;
-    for (int p0 = 0; p0 < npass; p0 += kBatch) {
+    for (int r0 = 0; r0 < n; r0 += 4 * kBatch) {
       float4 v[kBatch][C];
 #pragma unroll
       for (int u = 0; u < kBatch; ++u) {
-        int r = (p0 + u) * 4 + team;
-        int rid = __shfl_sync(FULL, id, r & 31);
-        bool ok = (p0 + u < npass) && (r < n);
-        const float4* row = t.vec + (size_t)(ok ? rid : 0) * t.stride4;
+        // rows past n are folded onto row 0 of the list: a harmless repeated load whose result nobody selects
+        const int r = r0 + 4 * u + team;
+        const int rid = __shfl_sync(FULL, id, r < n ? r : 0);
+        const float4* row = t.vec + (size_t)rid * t.stride4;
 #pragma unroll
         for (int c = 0; c < C; ++c) {
-          int ch = tl + 8 * c;
-          v[u][c] = (ok && ch < t.nchunk) ? ldg4(row + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const int ch = tl + 8 * c;
+          // only the last chunk column can lie past the end of the row
+          v[u][c] = (c < C - 1 || ch < t.nchunk) ? ldg4(row + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
       }
 #pragma unroll
       for (int u = 0; u < kBatch; ++u) {
-        if (p0 + u < npass) {  // warp-uniform
+        if (u == 0 || r0 + 4 * u < n) {  // warp-uniform
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-          for (int c = 0; c < C; ++c) fma4(acc, q[c], v[u][c], t.dist_type);
+          for (int c = 0; c < C; ++c) fma4(acc, q[c], v[u][c], kDot ? DIST_DOT : DIST_L2);
           float s = fold4(acc);
           s += __shfl_xor_sync(FULL, s, 4);
           s += __shfl_xor_sync(FULL, s, 2);
           s += __shfl_xor_sync(FULL, s, 1);
-          if (t.dist_type == DIST_DOT) s = -s;
-          float mine = __shfl_sync(FULL, s, (lane & 3) << 3);
-          if ((lane >> 2) == p0 + u) result = mine;
+          if (kDot) s = -s;
+          const float mine = __shfl_sync(FULL, s, (lane & 3) << 3);
+          if ((lane >> 2) == (r0 >> 2) + u) result = mine;
         }
       }
     }

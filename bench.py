@@ -34,6 +34,7 @@ sys.path.insert(0, ROOT)
 WORKLOAD = "angular_full"
 RECALL_TARGET = 0.95
 FLUSH_BYTES = 256 << 20  # > 126 MB L2
+NCU_TRAFFIC_BYTES = 3.468e9  # per launch of 10 000 queries at ef_search 300, from the ncu capture under profiles/
 
 
 def parse():
@@ -315,8 +316,12 @@ def run_ours(args, rank, world, local_rank):
   bq = algorithmic_bytes_per_query(counts["evals"], counts["expansions"], counts["sweeps"], d, opt["max_m"],
                                    opt["max_m0"], topk)
   achieved = bq * nq / (ms_dev / args.steps * 1e-3) / 1e9
+  # DRAM bytes of one launch from the committed ncu capture of this exact workload (dram__bytes_read.sum +
+  # dram__bytes_write.sum, profiles/knn_search_kernel_angular_full.md); null for any other shape
+  traffic = NCU_TRAFFIC_BYTES if (args.n is None and args.nq is None and ef == 300) else None
   line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                      "traffic": None, "peak_source": peak_kind, "bytes_per_query": bq, "counts": counts}
+                      "traffic": traffic, "algorithmic_bytes_per_launch": bq * nq, "peak_source": peak_kind,
+                      "bytes_per_query": bq, "counts": counts}
   if cpu is not None:
     line["cpu_baseline"] = cpu
   print(json.dumps(line), flush=True)

@@ -6,12 +6,16 @@
  * independent plain-C restatement of the algorithm, and so that a host-CPU
  * baseline can be timed beside the GPU numbers.
  *
- * Pinning status: the reference project ships no golden vectors or tests for
- * this path, and the CPU library it names as its correctness reference
- * (hnswlib, un-pinned in examples/requirements.txt:3) is not part of its
- * source tree.  Until fixtures produced by the reference's own kernels are
- * committed next to the tests, parity with the reference is UNPINNED; the
- * level-draw and index-file known answers are pinned separately in the tests.
+ * Pinning status: PINNED against the reference's own code.  The reference ships
+ * no golden vectors, so fixtures were produced by running it: level draws by
+ * executing the body of its set_random_levels (cuhnsw/pyhnsw.py:65-71), search
+ * results and index files by its unmodified CUDA sources compiled for sm_100
+ * and run on a B200 (generators and fixtures sit under tests/golden/).  On
+ * continuous data this oracle returns exactly the reference's ids; on data with
+ * exact distance ties only tie-independent facts can agree, because the
+ * reference orders ties by heap position.  Parity with hnswlib proper (the CPU
+ * library the reference names, examples/requirements.txt:3) stays unpinned: it
+ * is not part of the reference's tree and not installable offline.
  *
  * What each function follows in the reference (paths inside that project):
  *   canonical distance       cpp/include/cuda_dist_kernels.cuh:31-124

@@ -215,6 +215,9 @@ __global__ void __launch_bounds__(kBuildWarps * 32, Dist::kBuildMinCtas) build_s
   WarpList wl;
   SelBuf sel;
   bind_warp(smem, p.per_warp, L.g, p.cap, L.vsize, de, wl, sel);
+  // the shared-memory block is laid out for p.cap keys (at least a full row plus one, which the
+  // reverse-link kernel needs); the search itself keeps ef_construction keys
+  wl.cap = L.ef_construction;
   WalkCounters wc{0, 0, 0, 0};
   for (;;) {
     long long t = 0;

@@ -212,6 +212,29 @@ def test_built_graph_bit_exact_with_oracle_on_the_same_batch_schedule(name, n, c
   assert_same_bits(dist, odist)
 
 
+@pytest.mark.parametrize("d,max_m,max_m0,efc,dist_type", [(7, 20, 40, 60, "l2"), (33, 32, 64, 100, "dot"),
+                                                          (130, 5, 9, 300, "l2"), (1, 4, 8, 30, "l2")])
+def test_unusual_shapes_build_and_search_bit_exact(d, max_m, max_m0, efc, dist_type):
+  """Rows wider than one warp (max_m0 > 32), link budgets that are not multiples of 8, odd dimensions."""
+  rng = np.random.default_rng(d * 1000 + max_m0)
+  n = 3000
+  base = rng.standard_normal((n, d)).astype(np.float32)
+  q = rng.standard_normal((150, d)).astype(np.float32)
+  opt = dict(dist_type=dist_type, max_m=max_m, max_m0=max_m0, ef_construction=efc, seed=5, batch_max=200)
+  eng = CuHNSW(engine_options(opt))
+  eng.set_data(base)
+  eng.build()
+  levels, rows0, rows_u = eng.obj.get_graph()
+  assert (levels == ds.random_levels(n, 5, 1 / np.log(max_m))).all()  # level_mult defaults to 1 / ln(max_m)
+  g = oracle.build_graph(base, levels, max_m, max_m0, dist_type, efc, 0.25, False, bmax=200)
+  assert (rows0 == g.rows0).all() and (rows_u[:g.rowsU.shape[0]] == g.rowsU).all()
+  for ef in (10, 90):
+    ids, dist, found = eng.search_knn(q, 10, ef)
+    oids, odist, ofound = oracle.search(g, q, 10, ef)
+    assert (ids == oids).all() and (found == ofound).all()
+    assert_same_bits(dist, odist)
+
+
 def test_build_quality_not_below_reference_kernels(golden_dir):
   """recall@10 on the 100 000-point workload vs what the reference's own build reached with the
   same options on a B200 (tests/golden/ref_quality.json), tolerance 0.005; and vs the oracle's

@@ -99,6 +99,15 @@ class ClockSampler:
             "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def host_threads():
+  """Host cores this process may use.  torchrun exports OMP_NUM_THREADS=1, which would otherwise
+  throttle the CPU arm to one thread; the count is passed to the oracle explicitly."""
+  try:
+    return max(1, len(os.sched_getaffinity(0)))
+  except AttributeError:
+    return max(1, os.cpu_count() or 1)
+
+
 def measured_peak():
   path = os.path.join(ROOT, "MEASURED_PEAKS.json")
   try:
@@ -143,7 +152,7 @@ def run_reference(args, rank, world):
   base, queries, spec = ds.make(WORKLOAD, n=args.n, nq=args.nq)
   opt, topk = spec["opt"], spec["topk"]
   n, d = base.shape
-  threads = oracle.max_threads()
+  threads = host_threads()
   try:
     oracle.build(native=True)
     native = True
@@ -340,7 +349,7 @@ def cpu_baseline(engine, base, queries, spec, ef, seconds, counts):
     native = False
   g = oracle_graph_from_engine(engine, base, spec)
   topk = spec["topk"]
-  threads = oracle.max_threads()
+  threads = host_threads()
   _, _, _, cnt = oracle.search(g, queries, topk, ef, counters=True, nthreads=threads, native=native)
   exact = {"evals": float(cnt[:, 0].mean()), "expansions": float(cnt[:, 1].mean()), "sweeps": float(cnt[:, 2].mean()),
            "source": "CPU restatement, distinct evaluations, first query batch",

@@ -69,6 +69,7 @@ EXTENSIONS = {
   "batch_max": (int, 0),
   "ramp_div": (int, 16),
   "device_id": (int, -1),
+  "search_team": (int, -1),
 }
 ALIASES = {"heuristic_coff": "heuristic_coef"}
 

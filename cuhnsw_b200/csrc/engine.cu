@@ -126,6 +126,7 @@ int Engine::Init(const char* opt_path) {
   o.visited_list_size = (int)js.number("visited_list_size", o.visited_list_size);
   o.nrz = js.boolean("nrz", o.nrz);
   o.reverse_cand = js.boolean("reverse_cand", o.reverse_cand);
+  o.search_team = (int)js.number("search_team", o.search_team);
   // the reference's schema spells it heuristic_coef, its README heuristic_coff
   o.heuristic_coef = js.number("heuristic_coef", js.number("heuristic_coff", o.heuristic_coef));
   o.batch_max = (long long)js.number("batch_max", (double)o.batch_max);
@@ -412,6 +413,7 @@ int Engine::SearchGraphDevice(const float* d_q, long long nq, int topk, int ef, 
   p.ef = ef;
   p.vsize = vsize;
   p.reverse_cand = opt_.reverse_cand ? 1 : 0;
+  p.team = opt_.search_team;
   p.smem_per_warp = 0;
   p.labels = labelled_ ? labels_d_.get() : nullptr;
   p.out_ids = d_nns;
@@ -478,6 +480,7 @@ int Engine::SearchGraphStatic(const float* q, long long nq, int topk, int ef, in
   p.ef = ef;
   p.vsize = vsize;
   p.reverse_cand = opt_.reverse_cand ? 1 : 0;
+  p.team = opt_.search_team;
   p.smem_per_warp = 0;
   p.labels = labelled_ ? labels_d_.get() : nullptr;
   p.out_ids = nullptr;

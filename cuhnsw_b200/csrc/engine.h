@@ -40,6 +40,7 @@ struct Options {
   int visited_list_size = 8192;
   bool nrz = false;
   bool reverse_cand = false;
+  int search_team = -1;  // d > 128: 1 = CTA per query, 0 = warp per query, -1 = chosen by batch size
   double heuristic_coef = 0.25;
   // extensions (absent from the reference's schema; optional keys of the option file)
   long long batch_max = 0;  // nodes per insertion batch; 0 = hyper_threads * (SMs * 128 / block_dim)

@@ -30,6 +30,7 @@ struct SearchParams {
   int ef;
   int vsize;             // visited table entries per warp (power of two)
   int reverse_cand;      // expand the farthest unexpanded key first
+  int team = -1;         // rows wider than 128 floats: 1 = one CTA per query, 0 = one warp per query, -1 = by batch size
   int smem_per_warp;     // filled by the launcher
   const int* labels;     // optional id -> label map (index loaded from a file)
   int* out_ids;          // nq x topk
@@ -41,6 +42,8 @@ struct SearchParams {
 
 cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream);
 size_t search_smem_per_cta(int d, int ef, int vsize, long long n);
+// d > 128 only: one CTA of four warps per query, the extra warps share the distance evaluations
+cudaError_t launch_search_team(const SearchParams& p, int sm_count, cudaStream_t stream);
 // search whose device staging and work ticket live in a fixed file-scope device array (no allocation)
 size_t search_static_capacity();
 size_t search_static_bytes(long long nq, int d, int topk);

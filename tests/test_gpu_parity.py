@@ -79,6 +79,30 @@ def test_search_ids_and_distances_bit_exact(name, n, nq, efs, tmp_path):
   assert ds.recall(ids, truth) > 0.9
 
 
+@pytest.mark.parametrize("d,dist_type", [(960, "l2"), (200, "dot"), (129, "l2")])
+def test_wide_rows_every_search_kernel_gives_the_oracle_answer(d, dist_type, tmp_path):
+  """Rows wider than 128 floats have three kernels: a CTA of four warps per query, a warp per query with
+  deep load batches (few queries), a warp per query with shallow batches (many queries)."""
+  rng = np.random.default_rng(d)
+  n, nq = 3000, 120
+  base = rng.standard_normal((n, d)).astype(np.float32)
+  q = rng.standard_normal((nq, d)).astype(np.float32)
+  opt = {"dist_type": dist_type, "max_m": 12, "max_m0": 24, "ef_construction": 100, "level_mult": 0.4, "seed": 5}
+  levels = ds.random_levels(n, opt["seed"], opt["level_mult"])
+  g = oracle.build_graph(base, levels, 12, 24, dist_type, 100, bmax=512)
+  want = {ef: oracle.search(g, q, 10, ef) for ef in (10, 100, 400)}
+  for team in (1, 0, -1):
+    eng = engine_from_oracle_graph(g, opt, tmp_path, search_team=team)
+    for ef, (oids, odist, ofound) in want.items():
+      ids, dist, found = eng.search_knn(q, 10, ef)
+      assert (ids == oids).all() and (found == ofound).all(), f"team={team} ef={ef}"
+      assert_same_bits(dist, odist)
+    # 15 copies of the batch: more queries than ten per SM, the many-queries kernel (team = 0, -1)
+    ids, dist, found = eng.search_knn(np.tile(q, (15, 1)), 10, 100)
+    assert (ids == np.tile(want[100][0], (15, 1))).all()
+    assert_same_bits(dist, np.tile(want[100][1], (15, 1)))
+
+
 def test_search_equals_reference_kernels_on_their_golden_vectors(golden_dir):
   """The reference's own LoadIndex + SearchGraph output on the same file, queries and ef."""
   z = np.load(os.path.join(golden_dir, "ref_search_angular.npz"))

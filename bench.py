@@ -5,11 +5,16 @@ ef_construction 110, 10 000 queries per GPU per step), plus build seconds per
 million vectors.  Synthetic data (seeded mixture of Gaussians with the shape of
 glove-50-angular); nothing is read from disk.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 One process per GPU (torchrun sets RANK/LOCAL_RANK/WORLD_SIZE).  Every rank holds
 a replica of the index and searches its own query batches (weak scaling, no
 data-path collective).  Rank 0 prints ONE JSON line.
+
+--workload runs one of the other workloads of cuhnsw_b200/datasets.py under the same protocol (the default
+is the headline).  "sharded_100m" on N > 1 GPUs is the base-sharded mode: rank r builds shard r (12.5 M
+rows), every rank searches ALL queries of a step in its shard, the per-shard top-k rows are exchanged with
+one NCCL all-gather and merged by (distance, id) on the device; value = queries answered over the union.
 
   value     queries/s over all ranks, queries and results resident in HBM,
             CUDA events around the search launch, max over ranks
@@ -31,7 +36,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-WORKLOAD = "angular_full"
+HEADLINE = "angular_full"
 RECALL_TARGET = 0.95
 FLUSH_BYTES = 256 << 20  # > 126 MB L2
 NCU_TRAFFIC_BYTES = 3.468e9  # per launch of 10 000 queries at ef_search 300, from the ncu capture under profiles/
@@ -46,6 +51,8 @@ def parse():
   ap.add_argument("--n", type=int, default=None, help="override base size (debugging only; invalid as a bench number)")
   ap.add_argument("--nq", type=int, default=None)
   ap.add_argument("--cpu-seconds", type=float, default=12.0)
+  ap.add_argument("--workload", default=HEADLINE, help="other workloads are side measurements, not the headline")
+  ap.add_argument("--recall-queries", type=int, default=10000, help="queries of the first batch used for recall")
   return ap.parse_args()
 
 
@@ -149,7 +156,10 @@ def run_reference(args, rank, world):
     return
   import oracle
   from cuhnsw_b200 import datasets as ds
-  base, queries, spec = ds.make(WORKLOAD, n=args.n, nq=args.nq)
+  n_arg, nq_arg = args.n, args.nq
+  if args.workload == "sharded_100m" and n_arg is None:
+    n_arg, nq_arg = 1_000_000, nq_arg or 10_000  # a 12.5 M CPU build takes minutes: 1 M sub-sample of one shard
+  base, queries, spec = ds.make(args.workload, n=n_arg, nq=nq_arg)
   opt, topk = spec["opt"], spec["topk"]
   n, d = base.shape
   threads = host_threads()
@@ -184,7 +194,7 @@ def run_reference(args, rank, world):
     "impl": "reference", "metric": "batch-search QPS at recall@10>=0.95", "value": qps, "unit": "queries/s",
     "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3,
     "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-    "config": {"workload": WORKLOAD, "n": int(n), "d": int(d), "queries_per_step": nq_step, "topk": topk,
+    "config": {"workload": args.workload, "n": int(n), "d": int(d), "queries_per_step": nq_step, "topk": topk,
                "ef_search": ef, "recall_at_10": recalls[ef], "recall_sweep": {str(k): v for k, v in recalls.items()},
                "max_m": opt["max_m"], "max_m0": opt["max_m0"], "ef_construction": opt["ef_construction"]},
     "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": threads, "kind": "port", "sample": sample_txt},
@@ -207,7 +217,11 @@ def run_ours(args, rank, world, local_rank):
   if world > 1:
     dist.init_process_group("nccl", device_id=dev)
 
-  base, queries0, spec = ds.make(WORKLOAD, n=args.n, nq=args.nq)
+  sharded = args.workload == "sharded_100m" and world > 1
+  # sharded: rank r holds shard r (its own seed); every rank sees the same query batches
+  base, queries0, spec = ds.make(args.workload, n=args.n, nq=args.nq, seed_offset=rank if sharded else 0)
+  if sharded:
+    queries0 = ds.make_queries(args.workload, queries0.shape[0], 0)
   opt, topk = dict(spec["opt"]), spec["topk"]
   n, d = base.shape
   nq = queries0.shape[0]
@@ -219,23 +233,51 @@ def run_ours(args, rank, world, local_rank):
   engine.obj.set_stream(torch.cuda.current_stream().cuda_stream)
 
   # ef_search: smallest value of the sweep that reaches the recall target on this index
-  truth = ds.ground_truth(base, queries0, topk, opt["dist_type"], device=dev)
+  nr = min(nq, args.recall_queries)
+  searcher = None
+  if sharded:
+    from cuhnsw_b200 import multi
+    id_offset = rank * n
+
+    def local_search(q, k, ef_):
+      out = (torch.empty((len(q), k), dtype=torch.int32, device=dev), torch.empty((len(q), k), device=dev),
+             torch.empty((len(q),), dtype=torch.int32, device=dev))
+      engine.obj.search_knn_device(q.data_ptr(), len(q), k, ef_, *[t.data_ptr() for t in out])
+      return out
+
+    searcher = multi.ShardedSearcher(local_search, id_offset, rank, world, device_merge=multi.device_merge)
+    # exact answer over the union: exact top-k per shard, the same exchange and merge
+    tids, tdist = ds.ground_truth(base, queries0[:nr], topk, opt["dist_type"], device=dev, with_distances=True)
+    tids = torch.from_numpy(tids).to(dev) + id_offset
+    truth = multi.device_merge(torch.stack(multi.gather_rows(tids, world)),
+                               torch.stack(multi.gather_rows(torch.from_numpy(tdist).to(dev), world)),
+                               topk)[0].cpu().numpy()
+  else:
+    truth = ds.ground_truth(base, queries0[:nr], topk, opt["dist_type"], device=dev)
   recalls = {}
   for ef in spec["ef_sweep"]:
-    ids, _, _ = engine.search_knn(queries0, topk, ef)
+    if sharded:
+      ids = searcher.search(torch.from_numpy(queries0[:nr]).to(dev), topk, ef)[0].cpu().numpy()
+    else:
+      ids, _, _ = engine.search_knn(queries0[:nr], topk, ef)
     recalls[ef] = ds.recall(ids, truth)
   ef = pick_ef(recalls)
 
   total = args.warmup + args.steps
-  # distinct query batches per step and per rank; batch 0 of rank 0 is the recall batch
-  batches = [queries0 if (s == 0 and rank == 0) else ds.make_queries(WORKLOAD, nq, 1 + s + 1000 * rank)
-             for s in range(total)]
-  q_dev = [torch.from_numpy(b).to(dev) for b in batches]
+  # distinct query batches per step (and per rank when the index is replicated); batch 0 of rank 0 is the
+  # recall batch.  Large batches (100 000 queries) cycle through four distinct ones to bound memory.
+  distinct = total if nq * d * 4 * total <= (1 << 30) else 4
+  made = [queries0 if (s == 0 and (rank == 0 or sharded)) else
+          ds.make_queries(args.workload, nq, 1 + s + (0 if sharded else 1000 * rank)) for s in range(distinct)]
+  batches = [made[s % distinct] for s in range(total)]
+  q_dev_made = [torch.from_numpy(b).to(dev) for b in made]
+  q_dev = [q_dev_made[s % distinct] for s in range(total)]
   ids_dev = torch.empty((nq, topk), dtype=torch.int32, device=dev)
   dist_dev = torch.empty((nq, topk), dtype=torch.float32, device=dev)
   found_dev = torch.empty((nq,), dtype=torch.int32, device=dev)
   flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
-  q_pin = [torch.from_numpy(b).pin_memory() for b in batches]
+  q_pin_made = [torch.from_numpy(b).pin_memory() for b in made]
+  q_pin = [q_pin_made[s % distinct] for s in range(total)]
   ids_pin = torch.empty((nq, topk), dtype=torch.int32).pin_memory()
   dist_pin = torch.empty((nq, topk), dtype=torch.float32).pin_memory()
   found_pin = torch.empty((nq,), dtype=torch.int32).pin_memory()
@@ -250,8 +292,11 @@ def run_ours(args, rank, world, local_rank):
     flush.zero_()  # evict the index from L2 between steps (not timed)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    engine.obj.search_knn_device(q_dev[s].data_ptr(), nq, topk, ef, ids_dev.data_ptr(), dist_dev.data_ptr(),
-                                 found_dev.data_ptr())
+    if sharded:
+      searcher.search(q_dev[s], topk, ef)  # local search, all-gather, merge: all on this stream
+    else:
+      engine.obj.search_knn_device(q_dev[s].data_ptr(), nq, topk, ef, ids_dev.data_ptr(), dist_dev.data_ptr(),
+                                   found_dev.data_ptr())
     b.record()
     return a, b
 
@@ -259,7 +304,13 @@ def run_ours(args, rank, world, local_rank):
     flush.zero_()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    engine.obj.search_knn(q_pin[s].numpy(), topk, ef, ids_pin.numpy(), dist_pin.numpy(), found_pin.numpy())
+    if sharded:
+      out = searcher.search(q_pin[s].to(dev, non_blocking=True), topk, ef)
+      for src, dst in zip(out, (ids_pin, dist_pin, found_pin)):
+        dst.copy_(src, non_blocking=True)
+      torch.cuda.current_stream().synchronize()  # the caller holds the answer here
+    else:
+      engine.obj.search_knn(q_pin[s].numpy(), topk, ef, ids_pin.numpy(), dist_pin.numpy(), found_pin.numpy())
     b.record()
     return a, b
 
@@ -285,7 +336,7 @@ def run_ours(args, rank, world, local_rank):
   ms_e2e = timed(step_host)
   clocks = sampler.stop() if rank == 0 else None
   # sanity of the last timed result: sorted rows, full rows
-  assert int(found_pin.min()) == min(topk, n), "search returned short rows"
+  assert int(found_pin.min()) == min(topk, n * (world if sharded else 1)), "search returned short rows"
   assert bool((dist_pin[:, 1:] >= dist_pin[:, :-1]).all()), "rows are not ascending"
 
   if rank != 0:
@@ -293,7 +344,7 @@ def run_ours(args, rank, world, local_rank):
       dist.destroy_process_group()
     return
 
-  total_q = world * nq * args.steps
+  total_q = (1 if sharded else world) * nq * args.steps  # sharded: every rank works on the same queries
   value = total_q / (ms_dev * 1e-3)
   e2e = total_q / (ms_e2e * 1e-3)
   peak, peak_kind = measured_peak()
@@ -301,14 +352,17 @@ def run_ours(args, rank, world, local_rank):
     "metric": "batch-search QPS at recall@10>=0.95", "value": value, "unit": "queries/s", "n_gpus": world,
     "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
     "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-    "config": {"workload": WORKLOAD, "n": int(n), "d": int(d), "queries_per_step_per_gpu": int(nq), "topk": topk,
+    "config": {"workload": args.workload, "n": int(n) * (world if sharded else 1), "d": int(d),
+               "queries_per_step_per_gpu": int(nq), "topk": topk,
                "ef_search": ef, "recall_at_10": recalls[ef], "recall_sweep": {str(k): v for k, v in recalls.items()},
                "max_m": opt["max_m"], "max_m0": opt["max_m0"], "ef_construction": opt["ef_construction"],
-               "parallelism": f"replica x{world}, queries split", "l2": "flushed between steps (256 MB write)",
-               "index_bytes": int(n * (56 * 4 + 24 * 4))},
+               "parallelism": (f"base sharded x{world} ({n} rows per GPU), all queries on every GPU, all-gather + merge"
+                               if sharded else f"replica x{world}, queries split"),
+               "l2": "flushed between steps (256 MB write)", "recall_queries": int(nr),
+               "index_bytes_per_gpu": int(n * ((d + 7) // 8 * 8 * 4 + (opt["max_m0"] + 7) // 8 * 8 * 4))},
     "e2e": {"value": e2e, "unit": "queries/s", "h2d_bytes_per_step": int(nq * d * 4),
             "d2h_bytes_per_step": int(nq * topk * 8 + nq * 4), "ms_per_step": ms_e2e / args.steps},
-    "gpu_launches": args.steps,
+    "gpu_launches": args.steps * (2 if sharded else 1),  # search kernel (+ merge kernel when sharded)
     "build_sec_per_1M": build_s / (n / 1e6), "build_seconds": build_s,
     "clocks": clocks,
   }
@@ -327,7 +381,8 @@ def run_ours(args, rank, world, local_rank):
   achieved = bq * nq / (ms_dev / args.steps * 1e-3) / 1e9
   # DRAM bytes of one launch from the committed ncu capture of this exact workload (dram__bytes_read.sum +
   # dram__bytes_write.sum, profiles/knn_search_kernel_angular_full.md); null for any other shape
-  traffic = NCU_TRAFFIC_BYTES if (args.n is None and args.nq is None and ef == 300) else None
+  traffic = NCU_TRAFFIC_BYTES if (args.workload == HEADLINE and args.n is None and args.nq is None and
+                                  ef == 300) else None
   line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                       "traffic": traffic, "algorithmic_bytes_per_launch": bq * nq, "peak_source": peak_kind,
                       "bytes_per_query": bq, "counts": counts}

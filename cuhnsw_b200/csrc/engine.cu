@@ -261,7 +261,7 @@ GraphView Engine::View() const {
   return g;
 }
 
-int Engine::ResolveVsize(int cap, int* vsize) const {
+int Engine::ResolveVsize(int cap, long long nq, int* vsize) const {
   int v;
   if (opt_.visited_table_size > 0) {
     v = std::min(32768, std::max(64, next_pow2(opt_.visited_table_size)));
@@ -269,10 +269,16 @@ int Engine::ResolveVsize(int cap, int* vsize) const {
     // Largest table that still lets the kernel keep its target number of warps resident per SM
     // (the walk is latency bound: resident warps matter more than a few repeated evaluations),
     // but never below ~4 entries per list slot, where repeats explode.
-    const int warps = d_ <= 128 ? 32 : 16;
+    // Wide rows and few queries: the kernels chosen there keep 4 CTAs per SM resident whatever the table
+    // size, and a repeated evaluation re-reads kilobytes.  Measured on 1M x 960, 1000 queries, ef 500:
+    // 3576 evaluations per query and 5.67 ms with 2048 entries, 2099 and 4.98 ms with 16384.
+    const int kind = nq < 0 ? kSearchWarp
+                            : search_kernel_kind(d_, nq, opt_.search_team, opt_.reverse_cand ? 1 : 0, sm_count_);
+    const int warps = d_ <= 128 ? 32 : kind == kSearchTeam ? 4 : kind == kSearchWarpDeep ? 8 : 16;
+    const int top = kind == kSearchTeam ? 16384 : kind == kSearchWarpDeep ? 8192 : 4096;
     const long long budget = (long long)smem_optin_ / warps - 640;
     const int floor_entries = std::min(4096, std::max(512, next_pow2(4ll * cap)));
-    v = 4096;
+    v = top;
     while (v > floor_entries && (long long)search_smem_per_cta(d_, cap, v, n_) / 2 > budget) v >>= 1;
   }
   while (v > 64 && search_smem_per_cta(d_, cap, v, n_) + 4096 > smem_optin_) v >>= 1;
@@ -297,7 +303,7 @@ int Engine::BuildGraph() {
   bmax = std::max<long long>(1, std::min(bmax, n_));
   const int smax = std::max(stride0_, strideU_);
   int vsize = 0;
-  if (ResolveVsize(std::max(opt_.ef_construction, kMaxLinksHost + 8), &vsize) != kOk)
+  if (ResolveVsize(std::max(opt_.ef_construction, kMaxLinksHost + 8), -1, &vsize) != kOk)
     return Fail(kUnsupported, "ef_construction does not fit in shared memory");
   DevBuf<float> dist0, distU, st_dist;
   DevBuf<unsigned char> went;
@@ -404,7 +410,7 @@ int Engine::SearchGraphDevice(const float* d_q, long long nq, int topk, int ef, 
     return kOk;
   }
   int vsize = 0;
-  if (ResolveVsize(ef, &vsize) != kOk) return Fail(kUnsupported, "ef_search does not fit in shared memory");
+  if (ResolveVsize(ef, nq, &vsize) != kOk) return Fail(kUnsupported, "ef_search does not fit in shared memory");
   SearchParams p;
   p.g = View();
   p.queries = d_q;
@@ -471,7 +477,7 @@ int Engine::SearchGraphStatic(const float* q, long long nq, int topk, int ef, in
     return kOk;
   }
   int vsize = 0;
-  if (ResolveVsize(ef, &vsize) != kOk) return Fail(kUnsupported, "ef_search does not fit in shared memory");
+  if (ResolveVsize(ef, nq, &vsize) != kOk) return Fail(kUnsupported, "ef_search does not fit in shared memory");
   SearchParams p;
   p.g = View();
   p.queries = nullptr;

@@ -114,7 +114,7 @@ class Engine {
   int FailCuda(cudaError_t e, const char* what);
   int EnsureDevice();
   int AllocGraph();
-  int ResolveVsize(int requested_cap, int* vsize) const;
+  int ResolveVsize(int requested_cap, long long nq, int* vsize) const;  // nq < 0: construction
   GraphView View() const;
   void Log(int level, const char* fmt, ...) const;
 

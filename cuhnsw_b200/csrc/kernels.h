@@ -42,6 +42,9 @@ struct SearchParams {
 
 cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream);
 size_t search_smem_per_cta(int d, int ef, int vsize, long long n);
+// which search kernel a batch gets: rows <= 128 floats; wide rows with many / some / few queries
+enum SearchKernelKind { kSearchWarpSmall = 0, kSearchWarp = 1, kSearchWarpDeep = 2, kSearchTeam = 3 };
+int search_kernel_kind(int d, long long nq, int team, int reverse_cand, int sm_count);
 // d > 128 only: one CTA of four warps per query, the extra warps share the distance evaluations
 cudaError_t launch_search_team(const SearchParams& p, int sm_count, cudaStream_t stream);
 // search whose device staging and work ticket live in a fixed file-scope device array (no allocation)

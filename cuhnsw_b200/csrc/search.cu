@@ -106,6 +106,18 @@ size_t search_smem_per_cta(int d, int ef, int vsize, long long n) {
   return per_warp * kWarpsPerCta;
 }
 
+// Rows wider than 128 floats, fewer queries than warp slots: resident warps do not matter, the time of one
+// step does.  Up to 7 queries per SM one CTA of four warps per query shares the distance evaluations of every
+// step; up to 10 per SM one warp per query keeps 32 float4 loads in flight instead of 16.
+// Measured on 1M x 960 (ef 100 / 500): 100 queries 0.85 / 3.0 ms against 1.47 / 4.3 ms with one warp per
+// query, 1000 queries 1.48 / 5.9 against 1.74 / 6.0 ms, 1480 queries 1.79 / 7.2 against 2.17 / 6.8 ms.
+int search_kernel_kind(int d, long long nq, int team, int reverse_cand, int sm_count) {
+  if (d <= 128) return kSearchWarpSmall;
+  if (!reverse_cand && (team == 1 || (team < 0 && nq <= (long long)sm_count * 7))) return kSearchTeam;
+  if (nq <= (long long)sm_count * 10) return kSearchWarpDeep;
+  return kSearchWarp;
+}
+
 cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream) {
   if (p.nq <= 0) return cudaSuccess;
   const int d = p.g.d;
@@ -113,14 +125,11 @@ cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stre
   if (d <= 64) return launch_search_t<DistSmall<2>>(p, sm_count, stream);
   if (d <= 96) return launch_search_t<DistSmall<3>>(p, sm_count, stream);
   if (d <= 128) return launch_search_t<DistSmall<4>>(p, sm_count, stream);
-  // Fewer queries than warp slots: resident warps do not matter, the time of one step does.
-  // One CTA of four warps per query shares the distance evaluations of every step.
-  // Measured on 1M x 960 (ef 100 / 500): 100 queries 0.85 / 3.0 ms against 1.47 / 4.3 ms with one warp per
-  // query, 1000 queries 1.48 / 5.9 against 1.74 / 6.0 ms, 1480 queries 1.79 / 7.2 against 2.17 / 6.8 ms.
-  const bool few = p.nq <= (long long)sm_count * 10;
-  if (!p.reverse_cand && (p.team == 1 || (p.team < 0 && p.nq <= (long long)sm_count * 7)))
-    return launch_search_team(p, sm_count, stream);
-  if (few) return launch_search_t<DistLargeDeep>(p, sm_count, stream);
+  switch (search_kernel_kind(d, p.nq, p.team, p.reverse_cand, sm_count)) {
+    case kSearchTeam: return launch_search_team(p, sm_count, stream);
+    case kSearchWarpDeep: return launch_search_t<DistLargeDeep>(p, sm_count, stream);
+    default: break;
+  }
   return launch_search_t<DistLarge>(p, sm_count, stream);
 }
 

@@ -88,15 +88,16 @@ def make_queries(name, nq, seed_offset):
   return _draw(spec["kind"], c, spec["sigma"], nq, spec["qseed"] + 104729 * seed_offset)
 
 
-def ground_truth(base, queries, topk, dist_type, device="cpu", chunk=None):
-  """Exact top-k ids by brute force (float32 matmul in chunks; ties by id)."""
+def ground_truth(base, queries, topk, dist_type, device="cpu", chunk=None, with_distances=False):
+  """Exact top-k ids by brute force (float32 matmul in chunks; ties by id).  With
+  ``with_distances`` also the distances (L2: |b|^2 - 2 q.b + |q|^2), for merging shards."""
   import torch
   b = torch.as_tensor(base).to(device)
   q = torch.as_tensor(queries).to(device)
   n = b.shape[0]
   if chunk is None:
     chunk = max(1, int(2 ** 28 // max(n, 1)))
-  out = []
+  out, out_d = [], []
   bn = (b * b).sum(1) if dist_type == "l2" else None
   for s in range(0, q.shape[0], chunk):
     qq = q[s:s + chunk]
@@ -106,6 +107,10 @@ def ground_truth(base, queries, topk, dist_type, device="cpu", chunk=None):
     k = min(topk, n)
     vals, idx = torch.topk(dist, k, dim=1, largest=False, sorted=True)
     out.append(idx.to(torch.int32).cpu())
+    if with_distances:
+      out_d.append((vals + (qq * qq).sum(1, keepdim=True) if dist_type == "l2" else vals).cpu())
+  if with_distances:
+    return torch.cat(out).numpy(), torch.cat(out_d).numpy()
   return torch.cat(out).numpy()
 
 

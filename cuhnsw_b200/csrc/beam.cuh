@@ -127,8 +127,8 @@ struct WarpList {
     int pos = 0;
     bool dup = false;
     const int nch = (size + 31) >> 5;
-    if (__popc(km0) <= 2 && nch <= 32) {
-      // few newcomers: two-level search by the whole warp, one newcomer at a time
+    if (__popc(km0) <= 4 && nch <= 32) {
+      // up to four newcomers: two-level search by the whole warp, one newcomer at a time
       for (unsigned mm = km0; mm; mm &= mm - 1) {
         const int b = __ffs(mm) - 1;
         const unsigned long long kb = shfl64(key, b);
@@ -166,12 +166,16 @@ struct WarpList {
     if (m == 1) {
       // the common case: one newcomer, everything from its position on moves up by one
       minpos = __shfl_sync(FULL, pos, __ffs(km) - 1);
-      for (int hi = size; hi > minpos; hi -= 32) {  // windows [hi - 32, hi), top down
-        const int i = hi - 32 + lane;
-        const bool have = i >= minpos;
+      // windows of 64 keys, top down; both halves are read before either is written (a window's
+      // targets lie above everything a lower window reads)
+      for (int hi = size; hi > minpos; hi -= 64) {
+        const int i = hi - 32 + lane, i2 = i - 32;
+        const bool have = i >= minpos, have2 = i2 >= minpos;
         const unsigned long long v = have ? keys[i] : 0ull;
+        const unsigned long long v2 = have2 ? keys[i2] : 0ull;
         __syncwarp();
         if (have && i + 1 < cap) keys[i + 1] = v;
+        if (have2) keys[i2 + 1] = v2;  // i2 + 1 <= size - 32 < cap
       }
       if (keep) keys[pos] = key;  // pos < cap: either the list is not full or key < worst
     } else {
@@ -181,18 +185,27 @@ struct WarpList {
         const unsigned long long kb = shfl64(key, b);
         rk += (kb < key) ? 1 : 0;
       }
-      if (keep) spos[rk] = pos;
+      if (keep) spos[rk] = pos;  // newcomer positions, ascending
       __syncwarp();
       minpos = spos[0];
-      for (int hi = size; hi > minpos; hi -= 32) {
-        const int i = hi - 32 + lane;
-        const bool have = i >= minpos;
+      const int mypos = (lane < m) ? spos[lane] : 0x7fffffff;
+      for (int hi = size; hi > minpos; hi -= 64) {
+        // key i moves up by the number of newcomers placed at or before it; that number is the same for a
+        // whole window of 32 unless a newcomer lands inside it.  Two windows per turn, both read before
+        // either is written.
+        const int i = hi - 32 + lane, i2 = i - 32;
+        const bool have = i >= minpos, have2 = i2 >= minpos;
         const unsigned long long v = have ? keys[i] : 0ull;
-        int cnt = 0;
-        if (have)
-          for (int j = 0; j < m; ++j) cnt += (spos[j] <= i) ? 1 : 0;
+        const unsigned long long v2 = have2 ? keys[i2] : 0ull;
+        const int below2 = __popc(__ballot_sync(FULL, mypos <= hi - 64));
+        const int below = __popc(__ballot_sync(FULL, mypos <= hi - 32));
+        const int upto = __popc(__ballot_sync(FULL, mypos <= hi - 1));
+        int cnt = below, cnt2 = below2;
+        for (int j = below; j < upto; ++j) cnt += (spos[j] <= i) ? 1 : 0;
+        for (int j = below2; j < below; ++j) cnt2 += (spos[j] <= i2) ? 1 : 0;
         __syncwarp();
         if (have && i + cnt < cap) keys[i + cnt] = v;
+        if (have2 && i2 + cnt2 < cap) keys[i2 + cnt2] = v2;
       }
       if (keep && pos + rk < cap) keys[pos + rk] = key;
     }
@@ -292,9 +305,6 @@ __device__ __forceinline__ void beam_layer(Dist& de, WarpList& wl, const int* __
     int nid;
     if (cur == pf_node) {
       nid = pf_val;
-#ifdef HNSW_DEBUG_PF
-      wc.sweeps += 1;  // experiment: count prefetch hits in the sweeps slot
-#endif
     } else {
       nid = (lane < stride) ? __ldg(row + lane) : -1;
     }

@@ -70,6 +70,7 @@ EXTENSIONS = {
   "ramp_div": (int, 16),
   "device_id": (int, -1),
   "search_team": (int, -1),
+  "search_schedule": (bool, True),
 }
 ALIASES = {"heuristic_coff": "heuristic_coef"}
 

@@ -127,6 +127,7 @@ int Engine::Init(const char* opt_path) {
   o.nrz = js.boolean("nrz", o.nrz);
   o.reverse_cand = js.boolean("reverse_cand", o.reverse_cand);
   o.search_team = (int)js.number("search_team", o.search_team);
+  o.search_schedule = js.boolean("search_schedule", o.search_schedule);
   // the reference's schema spells it heuristic_coef, its README heuristic_coff
   o.heuristic_coef = js.number("heuristic_coef", js.number("heuristic_coff", o.heuristic_coef));
   o.batch_max = (long long)js.number("batch_max", (double)o.batch_max);
@@ -427,7 +428,33 @@ int Engine::SearchGraphDevice(const float* d_q, long long nq, int topk, int ef, 
   p.out_found = d_found;
   p.ticket = counters_.get();
   p.stats = stats_on_ ? counters_.get() + 4 : nullptr;
-  CU(launch_search(p, sm_count_, stream_));
+  SearchSchedule sched;
+  // the launcher schedules only batches of more than one wave of its kernel (4 CTAs to 32 warps per SM);
+  // below the smallest wave there is nothing to prepare
+  const bool schedule = nq > (long long)sm_count_ * 4 && opt_.search_schedule;
+  if (schedule && (rc = PrepareSchedule(nq, &sched)) != kOk) return rc;
+  CU(launch_search(p, sm_count_, stream_, schedule ? &sched : nullptr));
+  return kOk;
+}
+
+int Engine::PrepareSchedule(long long nq, SearchSchedule* s) {
+  if (nq > sched_capacity_) {
+    const long long cap = std::max<long long>(nq, 1024);
+    CU(sched_d_.reserve((size_t)cap * 6));
+    CU(sched_tmp_.reserve(search_schedule_tmp_bytes(cap)));
+    sched_capacity_ = cap;
+  }
+  unsigned* base = sched_d_.get();
+  const long long c = sched_capacity_;
+  s->capacity = c;
+  s->entry_node = reinterpret_cast<int*>(base);
+  s->entry_dist = reinterpret_cast<float*>(base + c);
+  s->keys = base + 2 * c;
+  s->keys_sorted = base + 3 * c;
+  s->index = reinterpret_cast<int*>(base + 4 * c);
+  s->order = reinterpret_cast<int*>(base + 5 * c);
+  s->sort_tmp = sched_tmp_.get();
+  s->sort_tmp_bytes = sched_tmp_.size();
   return kOk;
 }
 

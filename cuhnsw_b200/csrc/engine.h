@@ -41,6 +41,7 @@ struct Options {
   bool nrz = false;
   bool reverse_cand = false;
   int search_team = -1;  // d > 128: 1 = CTA per query, 0 = warp per query, -1 = chosen by batch size
+  bool search_schedule = true;  // batches of more than one wave: serve the queries with the farthest entry first
   double heuristic_coef = 0.25;
   // extensions (absent from the reference's schema; optional keys of the option file)
   long long batch_max = 0;  // nodes per insertion batch; 0 = hyper_threads * (SMs * 128 / block_dim)
@@ -145,6 +146,11 @@ class Engine {
   // grow-only staging for the host-pointer search path
   DevBuf<float> q_d_, dist_d_;
   DevBuf<int> ids_d_, found_d_;
+  // grow-only scratch of the longest-first schedule: six arrays of one word per query + sort storage
+  DevBuf<unsigned> sched_d_;
+  DevBuf<unsigned char> sched_tmp_;
+  long long sched_capacity_ = 0;
+  int PrepareSchedule(long long nq, SearchSchedule* s);
   double last_build_seconds_ = 0.0;
 };
 

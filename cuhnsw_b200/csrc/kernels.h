@@ -38,15 +38,45 @@ struct SearchParams {
   int* out_found;        // nq
   unsigned long long* ticket;  // work counter (zeroed by the launcher)
   unsigned long long* stats;   // optional: evals, expansions, sweeps, inserts
+  // filled by the launcher when it schedules the batch (see SearchSchedule): ticket t serves query order[t],
+  // whose greedy descent through the upper layers has already ended at entry_node / entry_dist
+  const int* order = nullptr;
+  const int* entry_node = nullptr;
+  const float* entry_dist = nullptr;
 };
 
-cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream);
+// Scratch for longest-first scheduling of a batch that needs more than one wave of warps.  A query's walk
+// is a chain of dependent steps; a few per cent of the queries need two to three times the median number
+// of steps, and when one of those starts in the last wave the whole launch waits for it.  Those queries
+// are the ones whose descent through the upper layers ends far from the query, so a first kernel does
+// that descent for every query, the queries are sorted by the distance it ended at (farthest first), and
+// the search kernel serves them in that order, starting from the stored entry.  Results do not depend on
+// the order.  All arrays hold `capacity` elements.
+struct SearchSchedule {
+  long long capacity;
+  int* entry_node;
+  float* entry_dist;
+  unsigned* keys;         // sort keys: farthest entry first
+  unsigned* keys_sorted;
+  int* index;             // 0, 1, 2, ...
+  int* order;             // query numbers, sorted
+  void* sort_tmp;
+  size_t sort_tmp_bytes;
+};
+size_t search_schedule_tmp_bytes(long long nq);
+
+// `sched` may be null: queries are then served in input order and descend inside the search kernel.
+cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream,
+                          const SearchSchedule* sched = nullptr);
 size_t search_smem_per_cta(int d, int ef, int vsize, long long n);
 // which search kernel a batch gets: rows <= 128 floats; wide rows with many / some / few queries
 enum SearchKernelKind { kSearchWarpSmall = 0, kSearchWarp = 1, kSearchWarpDeep = 2, kSearchTeam = 3 };
 int search_kernel_kind(int d, long long nq, int team, int reverse_cand, int sm_count);
 // d > 128 only: one CTA of four warps per query, the extra warps share the distance evaluations
-cudaError_t launch_search_team(const SearchParams& p, int sm_count, cudaStream_t stream);
+cudaError_t launch_search_team(const SearchParams& p, int sm_count, cudaStream_t stream,
+                               const SearchSchedule* sched = nullptr);
+// first stage of a scheduled search: descent of every query + sort; fills p.order / entry_node / entry_dist
+cudaError_t schedule_search(SearchParams& p, const SearchSchedule& sched, int sm_count, cudaStream_t stream);
 // search whose device staging and work ticket live in a fixed file-scope device array (no allocation)
 size_t search_static_capacity();
 size_t search_static_bytes(long long nq, int d, int topk);

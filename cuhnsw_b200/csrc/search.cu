@@ -5,6 +5,8 @@
 // (cpp/include/cuda_search_kernels.cuh:11-165, cpp/src/cuhnsw_build.cu:210-290),
 // which re-flatten and re-upload the graph on every call, launch once per
 // layer and keep the heap in global memory.
+#include <cub/device/device_radix_sort.cuh>
+
 #include "kernels.h"
 #include "beam.cuh"
 
@@ -30,13 +32,21 @@ knn_search_kernel(SearchParams p) {
     if (lane == 0) qi = (long long)atomicAdd(p.ticket, 1ull);
     qi = __shfl_sync(FULL, qi, 0);
     if (qi >= p.nq) break;
+    if (p.order) qi = __ldg(p.order + qi);
     de.load_query(p.queries + (size_t)qi * p.g.d);
     wl.reset();
-    int cur = p.g.enter_point;
-    float dcur = de.eval(cur, 1);
-    dcur = __shfl_sync(FULL, dcur, 0);
-    wc.evals += 1;
-    greedy_descent(de, wl.spos, p.g.rowsU, p.g.strideU, p.g.upper_base, p.g.max_level, 0, cur, dcur, wc);
+    int cur;
+    float dcur;
+    if (p.entry_node) {
+      cur = __ldg(p.entry_node + qi);
+      dcur = __ldg(p.entry_dist + qi);
+    } else {
+      cur = p.g.enter_point;
+      dcur = de.eval(cur, 1);
+      dcur = __shfl_sync(FULL, dcur, 0);
+      wc.evals += 1;
+      greedy_descent(de, wl.spos, p.g.rowsU, p.g.strideU, p.g.upper_base, p.g.max_level, 0, cur, dcur, wc);
+    }
     // layer 0: list = {entry}, visited = {entry} (cuda_search_kernels.cuh:108-112)
     wl.seed(mkkey(dcur, cur));
     wl.mark(cur);
@@ -67,17 +77,91 @@ knn_search_kernel(SearchParams p) {
   }
 }
 
-template <class Dist, bool kReverse>
-static cudaError_t launch_search_tr(const SearchParams& p0, int sm_count, cudaStream_t stream);
+// First stage of a scheduled search: one warp per query walks down the upper layers
+// (GetEntryPointsKernel of the reference, cuda_search_kernels.cuh:11-77, all layers in one launch) and
+// leaves where it ended, how far that is, and a sort key that puts the farthest entries first.
+template <class Dist>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) entry_kernel(SearchParams p, SearchSchedule s) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ int scratch[kWarpsPerCta][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long qi = (long long)blockIdx.x * kWarpsPerCta + warp;
+  if (qi >= p.nq) return;
+  Dist de;
+  VecTable tab{reinterpret_cast<const float4*>(p.g.vec), p.g.vstride / 4, (p.g.d + 3) / 4, p.g.d, p.g.dist_type};
+  de.init(tab, smem + (size_t)warp * Dist::smem_bytes(p.g.d));
+  WalkCounters wc{0, 0, 0, 0};
+  de.load_query(p.queries + (size_t)qi * p.g.d);
+  int cur = p.g.enter_point;
+  float dcur = de.eval(cur, 1);
+  dcur = __shfl_sync(FULL, dcur, 0);
+  wc.evals += 1;
+  greedy_descent(de, scratch[warp], p.g.rowsU, p.g.strideU, p.g.upper_base, p.g.max_level, 0, cur, dcur, wc);
+  if (lane == 0) {
+    s.entry_node[qi] = cur;
+    s.entry_dist[qi] = dcur;
+    s.keys[qi] = ~f2ord(dcur);
+    s.index[qi] = (int)qi;
+    if (p.stats) {
+      atomicAdd(p.stats + 0, (unsigned long long)wc.evals);
+      atomicAdd(p.stats + 2, (unsigned long long)wc.sweeps);
+    }
+  }
+}
 
 template <class Dist>
-static cudaError_t launch_search_t(const SearchParams& p0, int sm_count, cudaStream_t stream) {
-  return p0.reverse_cand ? launch_search_tr<Dist, true>(p0, sm_count, stream)
-                         : launch_search_tr<Dist, false>(p0, sm_count, stream);
+static cudaError_t launch_entry_t(const SearchParams& p, const SearchSchedule& s, cudaStream_t stream) {
+  const size_t smem = Dist::smem_bytes(p.g.d) * kWarpsPerCta;
+  auto kern = entry_kernel<Dist>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const long long grid = (p.nq + kWarpsPerCta - 1) / kWarpsPerCta;
+  kern<<<(unsigned)grid, kWarpsPerCta * 32, smem, stream>>>(p, s);
+  return cudaGetLastError();
+}
+
+size_t search_schedule_tmp_bytes(long long nq) {
+  size_t bytes = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, bytes, (const unsigned*)nullptr, (unsigned*)nullptr, (const int*)nullptr,
+                                  (int*)nullptr, (int)nq, 16, 32);
+  return bytes;
+}
+
+cudaError_t schedule_search(SearchParams& p, const SearchSchedule& s, int sm_count, cudaStream_t stream) {
+  (void)sm_count;
+  if (p.nq > s.capacity) return cudaErrorInvalidValue;
+  const int d = p.g.d;
+  cudaError_t e = d <= 32    ? launch_entry_t<DistSmall<1>>(p, s, stream)
+                  : d <= 64  ? launch_entry_t<DistSmall<2>>(p, s, stream)
+                  : d <= 96  ? launch_entry_t<DistSmall<3>>(p, s, stream)
+                  : d <= 128 ? launch_entry_t<DistSmall<4>>(p, s, stream)
+                             : launch_entry_t<DistLarge>(p, s, stream);
+  if (e != cudaSuccess) return e;
+  // the upper 16 bits of the key (sign, exponent, 7 bits of mantissa) order the queries finely enough
+  size_t bytes = s.sort_tmp_bytes;
+  e = cub::DeviceRadixSort::SortPairs(s.sort_tmp, bytes, (const unsigned*)s.keys, s.keys_sorted, (const int*)s.index,
+                                      s.order, (int)p.nq, 16, 32, stream);
+  if (e != cudaSuccess) return e;
+  p.order = s.order;
+  p.entry_node = s.entry_node;
+  p.entry_dist = s.entry_dist;
+  return cudaSuccess;
 }
 
 template <class Dist, bool kReverse>
-static cudaError_t launch_search_tr(const SearchParams& p0, int sm_count, cudaStream_t stream) {
+static cudaError_t launch_search_tr(const SearchParams& p0, int sm_count, cudaStream_t stream,
+                                    const SearchSchedule* sched);
+
+template <class Dist>
+static cudaError_t launch_search_t(const SearchParams& p0, int sm_count, cudaStream_t stream,
+                                   const SearchSchedule* sched) {
+  return p0.reverse_cand ? launch_search_tr<Dist, true>(p0, sm_count, stream, sched)
+                         : launch_search_tr<Dist, false>(p0, sm_count, stream, sched);
+}
+
+template <class Dist, bool kReverse>
+static cudaError_t launch_search_tr(const SearchParams& p0, int sm_count, cudaStream_t stream,
+                                    const SearchSchedule* sched) {
   SearchParams p = p0;
   size_t per_warp = Dist::smem_bytes(p.g.d) + WarpList::smem_bytes(p.ef, p.vsize, p.g.n);
   per_warp = (per_warp + 15) / 16 * 16;
@@ -94,6 +178,11 @@ static cudaError_t launch_search_tr(const SearchParams& p0, int sm_count, cudaSt
   long long grid = (long long)per_sm * sm_count;
   if (grid > want) grid = want;
   if (grid < 1) grid = 1;
+  // more queries than resident warps: start the long walks first
+  if (sched && p.nq > grid * kWarpsPerCta && p.nq <= sched->capacity) {
+    e = schedule_search(p, *sched, sm_count, stream);
+    if (e != cudaSuccess) return e;
+  }
   e = cudaMemsetAsync(p.ticket, 0, sizeof(unsigned long long), stream);
   if (e != cudaSuccess) return e;
   kern<<<(unsigned)grid, kWarpsPerCta * 32, smem, stream>>>(p);
@@ -118,19 +207,19 @@ int search_kernel_kind(int d, long long nq, int team, int reverse_cand, int sm_c
   return kSearchWarp;
 }
 
-cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream) {
+cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream, const SearchSchedule* sched) {
   if (p.nq <= 0) return cudaSuccess;
   const int d = p.g.d;
-  if (d <= 32) return launch_search_t<DistSmall<1>>(p, sm_count, stream);
-  if (d <= 64) return launch_search_t<DistSmall<2>>(p, sm_count, stream);
-  if (d <= 96) return launch_search_t<DistSmall<3>>(p, sm_count, stream);
-  if (d <= 128) return launch_search_t<DistSmall<4>>(p, sm_count, stream);
+  if (d <= 32) return launch_search_t<DistSmall<1>>(p, sm_count, stream, sched);
+  if (d <= 64) return launch_search_t<DistSmall<2>>(p, sm_count, stream, sched);
+  if (d <= 96) return launch_search_t<DistSmall<3>>(p, sm_count, stream, sched);
+  if (d <= 128) return launch_search_t<DistSmall<4>>(p, sm_count, stream, sched);
   switch (search_kernel_kind(d, p.nq, p.team, p.reverse_cand, sm_count)) {
-    case kSearchTeam: return launch_search_team(p, sm_count, stream);
-    case kSearchWarpDeep: return launch_search_t<DistLargeDeep>(p, sm_count, stream);
+    case kSearchTeam: return launch_search_team(p, sm_count, stream, sched);
+    case kSearchWarpDeep: return launch_search_t<DistLargeDeep>(p, sm_count, stream, sched);
     default: break;
   }
-  return launch_search_t<DistLarge>(p, sm_count, stream);
+  return launch_search_t<DistLarge>(p, sm_count, stream, sched);
 }
 
 }  // namespace hnsw

@@ -80,13 +80,21 @@ __global__ void __launch_bounds__(kTeamWarps * 32, 4) knn_search_team_kernel(Sea
     if (lane == 0) qi = (long long)atomicAdd(p.ticket, 1ull);
     qi = __shfl_sync(FULL, qi, 0);
     if (qi >= p.nq) break;
+    if (p.order) qi = __ldg(p.order + qi);
     de.load_query(p.queries + (size_t)qi * p.g.d);
     wl.reset();
-    int cur = p.g.enter_point;
-    float dcur = de.eval(cur, 1);
-    dcur = __shfl_sync(FULL, dcur, 0);
-    wc.evals += 1;
-    greedy_descent(de, wl.spos, p.g.rowsU, p.g.strideU, p.g.upper_base, p.g.max_level, 0, cur, dcur, wc);
+    int cur;
+    float dcur;
+    if (p.entry_node) {
+      cur = __ldg(p.entry_node + qi);
+      dcur = __ldg(p.entry_dist + qi);
+    } else {
+      cur = p.g.enter_point;
+      dcur = de.eval(cur, 1);
+      dcur = __shfl_sync(FULL, dcur, 0);
+      wc.evals += 1;
+      greedy_descent(de, wl.spos, p.g.rowsU, p.g.strideU, p.g.upper_base, p.g.max_level, 0, cur, dcur, wc);
+    }
     wl.seed(mkkey(dcur, cur));
     wl.mark(cur);
     beam_layer(de, wl, p.g.rows0, p.g.stride0, p.g.upper_base, 0, -1, wc);
@@ -121,7 +129,8 @@ size_t search_team_smem(int d, int ef, int vsize, long long n) {
   return (DistLarge::smem_bytes(d) + sizeof(TeamMailbox) + WarpList::smem_bytes(ef, vsize, n) + 15) / 16 * 16;
 }
 
-cudaError_t launch_search_team(const SearchParams& p0, int sm_count, cudaStream_t stream) {
+cudaError_t launch_search_team(const SearchParams& p0, int sm_count, cudaStream_t stream,
+                               const SearchSchedule* sched) {
   SearchParams p = p0;
   const size_t smem = search_team_smem(p.g.d, p.ef, p.vsize, p.g.n);
   p.smem_per_warp = (int)smem;
@@ -135,6 +144,10 @@ cudaError_t launch_search_team(const SearchParams& p0, int sm_count, cudaStream_
   long long grid = (long long)per_sm * sm_count;
   if (grid > p.nq) grid = p.nq;
   if (grid < 1) grid = 1;
+  if (sched && p.nq > grid && p.nq <= sched->capacity) {  // more queries than resident CTAs: long walks first
+    e = schedule_search(p, *sched, sm_count, stream);
+    if (e != cudaSuccess) return e;
+  }
   e = cudaMemsetAsync(p.ticket, 0, sizeof(unsigned long long), stream);
   if (e != cudaSuccess) return e;
   kern<<<(unsigned)grid, kTeamWarps * 32, smem, stream>>>(p);

@@ -103,6 +103,27 @@ def test_wide_rows_every_search_kernel_gives_the_oracle_answer(d, dist_type, tmp
     assert_same_bits(dist, np.tile(want[100][1], (15, 1)))
 
 
+@pytest.mark.parametrize("name,n,team", [("angular_toy", 20000, -1), ("highdim_l2", 3000, 1), ("highdim_l2", 3000, 0)])
+def test_batches_of_several_waves_are_served_longest_first_with_the_same_answers(name, n, team, tmp_path):
+  """More queries than resident warps: the engine first descends the upper layers for every query, sorts the
+  queries by the distance of the entry it found and serves the farthest first.  Answers must not change."""
+  base, q, opt = small_workload(name, n, 700)
+  levels = ds.random_levels(n, opt["seed"], opt["level_mult"])
+  g = oracle.build_graph(base, levels, opt["max_m"], opt["max_m0"], opt["dist_type"], opt["ef_construction"],
+                         bmax=512)
+  oids, odist, ofound = oracle.search(g, q, 10, 40)
+  reps = 8  # 5600 queries: more than 32 warps on each of 148 SMs
+  big = np.tile(q, (reps, 1))
+  for schedule in (True, False):
+    eng = engine_from_oracle_graph(g, opt, tmp_path, search_team=team, search_schedule=schedule)
+    eng.obj.enable_stats(True)
+    ids, dist, found = eng.search_knn(big, 10, 40)
+    stats = eng.obj.get_stats()
+    assert (ids == np.tile(oids, (reps, 1))).all() and (found == np.tile(ofound, reps)).all(), f"schedule={schedule}"
+    assert_same_bits(dist, np.tile(odist, (reps, 1)))
+    assert stats["expansions"] == reps * int(oracle.search(g, q, 10, 40, counters=True)[3][:, 1].sum())
+
+
 def test_search_equals_reference_kernels_on_their_golden_vectors(golden_dir):
   """The reference's own LoadIndex + SearchGraph output on the same file, queries and ef."""
   z = np.load(os.path.join(golden_dir, "ref_search_angular.npz"))

@@ -39,7 +39,7 @@ sys.path.insert(0, ROOT)
 HEADLINE = "angular_full"
 RECALL_TARGET = 0.95
 FLUSH_BYTES = 256 << 20  # > 126 MB L2
-NCU_TRAFFIC_BYTES = 3.468e9  # per launch of 10 000 queries at ef_search 300, from the ncu capture under profiles/
+NCU_TRAFFIC_BYTES = 3.150e9  # knn_search_kernel, per launch of 10 000 queries at ef_search 300, from the ncu capture under profiles/
 
 
 def parse():
@@ -362,7 +362,7 @@ def run_ours(args, rank, world, local_rank):
                "index_bytes_per_gpu": int(n * ((d + 7) // 8 * 8 * 4 + (opt["max_m0"] + 7) // 8 * 8 * 4))},
     "e2e": {"value": e2e, "unit": "queries/s", "h2d_bytes_per_step": int(nq * d * 4),
             "d2h_bytes_per_step": int(nq * topk * 8 + nq * 4), "ms_per_step": ms_e2e / args.steps},
-    "gpu_launches": args.steps * (2 if sharded else 1),  # search kernel (+ merge kernel when sharded)
+    "gpu_launches": args.steps * (3 if sharded else 2),  # entry kernel + search kernel (+ merge kernel when sharded); the sort between them is CUB
     "build_sec_per_1M": build_s / (n / 1e6), "build_seconds": build_s,
     "clocks": clocks,
   }

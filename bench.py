@@ -171,7 +171,7 @@ def run_reference(args, rank, world):
   levels = ds.random_levels(n, opt["seed"], opt["level_mult"])
   t0 = time.perf_counter()
   g = oracle.build_graph(base, levels, opt["max_m"], opt["max_m0"], opt["dist_type"], opt["ef_construction"],
-                         0.25, False, bmax=5920, ramp_div=16, nthreads=threads, native=native)
+                         0.25, False, bmax=23680, ramp_div=16, nthreads=threads, native=native)
   build_s = time.perf_counter() - t0
   sample = queries[:2000]
   truth = ds.ground_truth(base, sample, topk, opt["dist_type"])

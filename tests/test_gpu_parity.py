@@ -245,7 +245,7 @@ def test_built_graph_bit_exact_with_oracle_on_the_same_batch_schedule(name, n, c
   info = eng.obj.describe()
   levels, rows0, rows_u = eng.obj.get_graph()
   assert (levels == ds.random_levels(n, opt["seed"], opt["level_mult"])).all()
-  bmax = batch_max or int(10 * (info["sm_count"] * 128 // 32))
+  bmax = batch_max or int(4 * 10 * (info["sm_count"] * 128 // 32))
   g = oracle.build_graph(base, levels, opt["max_m"], opt["max_m0"], opt["dist_type"], opt["ef_construction"], coef,
                          save_remains, bmax=bmax, ramp_div=16)
   assert info["max_level"] == g.max_level and info["enter_point"] == g.enter_point
@@ -313,7 +313,7 @@ def test_degenerate_builds():
   eng.set_data(base)
   eng.build()
   levels, rows0, rows_u = eng.obj.get_graph()
-  g = oracle.build_graph(base, levels, 12, 24, "l2", 150, bmax=int(10 * eng.obj.describe()["sm_count"] * 4))
+  g = oracle.build_graph(base, levels, 12, 24, "l2", 150, bmax=int(4 * 10 * eng.obj.describe()["sm_count"] * 4))
   assert (rows0 == g.rows0).all()
   ids, dist, found = eng.search_knn(base[:4], 10, 50)
   assert (dist == 0).all() and (ids == oracle.search(g, base[:4], 10, 50)[0]).all()

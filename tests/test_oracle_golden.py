@@ -91,7 +91,7 @@ def test_oracle_build_quality_not_below_reference_kernels(golden_dir):
   assert len(base) == ref["n"]
   levels = ds.random_levels(len(base), opt["seed"], opt["level_mult"])
   truth = ds.ground_truth(base, q, 10, "dot")
-  for bmax in (1, 5920):
+  for bmax in (1, 23680):
     g = oracle.build_graph(base, levels, opt["max_m"], opt["max_m0"], "dot", opt["ef_construction"], 0.25, False,
                            bmax=bmax, ramp_div=16)
     for ef in (50, 100, 300):

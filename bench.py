@@ -53,6 +53,8 @@ def parse():
   ap.add_argument("--cpu-seconds", type=float, default=12.0)
   ap.add_argument("--workload", default=HEADLINE, help="other workloads are side measurements, not the headline")
   ap.add_argument("--recall-queries", type=int, default=10000, help="queries of the first batch used for recall")
+  ap.add_argument("--row-dtype", default="f32", choices=["f32", "f16"],
+                  help="storage type of the rows on the device (f16 is a side measurement; distances stay fp32)")
   return ap.parse_args()
 
 
@@ -124,10 +126,10 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
-def algorithmic_bytes_per_query(e, h, hu, d, max_m, max_m0, topk):
-  """Per-query gather bytes: E rows of 4d bytes, H layer-0 adjacency rows, Hu upper rows,
+def algorithmic_bytes_per_query(e, h, hu, d, max_m, max_m0, topk, elem_bytes=4):
+  """Per-query gather bytes: E rows of d elements, H layer-0 adjacency rows, Hu upper rows,
   the query itself and the result row."""
-  return e * 4 * d + h * 4 * (1 + max_m0) + hu * 4 * (1 + max_m) + 4 * d + 8 * topk
+  return e * elem_bytes * d + h * 4 * (1 + max_m0) + hu * 4 * (1 + max_m) + 4 * d + 8 * topk
 
 
 def pick_ef(recalls):
@@ -225,7 +227,11 @@ def run_ours(args, rank, world, local_rank):
   opt, topk = dict(spec["opt"]), spec["topk"]
   n, d = base.shape
   nq = queries0.shape[0]
-  engine = CuHNSW({**opt, "nrz": False, "c_log_level": 1, "py_log_level": 1})
+  engine = CuHNSW({**opt, "nrz": False, "c_log_level": 1, "py_log_level": 1, "row_dtype": args.row_dtype})
+  if args.row_dtype == "f16":
+    stored = base.astype(np.float16).astype(np.float32)  # what the device holds; the CPU arm searches the same values
+  else:
+    stored = base
   engine.set_data(base)
   t0 = time.perf_counter()
   engine.build()
@@ -358,8 +364,9 @@ def run_ours(args, rank, world, local_rank):
                "max_m": opt["max_m"], "max_m0": opt["max_m0"], "ef_construction": opt["ef_construction"],
                "parallelism": (f"base sharded x{world} ({n} rows per GPU), all queries on every GPU, all-gather + merge"
                                if sharded else f"replica x{world}, queries split"),
-               "l2": "flushed between steps (256 MB write)", "recall_queries": int(nr),
-               "index_bytes_per_gpu": int(n * ((d + 7) // 8 * 8 * 4 + (opt["max_m0"] + 7) // 8 * 8 * 4))},
+               "l2": "flushed between steps (256 MB write)", "recall_queries": int(nr), "row_dtype": args.row_dtype,
+               "index_bytes_per_gpu": int(n * ((d + 7) // 8 * 8 * (2 if args.row_dtype == "f16" else 4) +
+                                               (opt["max_m0"] + 7) // 8 * 8 * 4))},
     "e2e": {"value": e2e, "unit": "queries/s", "h2d_bytes_per_step": int(nq * d * 4),
             "d2h_bytes_per_step": int(nq * topk * 8 + nq * 4), "ms_per_step": ms_e2e / args.steps},
     "gpu_launches": args.steps * (3 if sharded else 2),  # entry kernel + search kernel (+ merge kernel when sharded); the sort between them is CUB
@@ -373,16 +380,16 @@ def run_ours(args, rank, world, local_rank):
   cpu = None
   if world == 1:
     try:
-      cpu, counts = cpu_baseline(engine, base, queries0, spec, ef, args.cpu_seconds, counts)
+      cpu, counts = cpu_baseline(engine, stored, queries0, spec, ef, args.cpu_seconds, counts)
     except Exception as exc:  # pylint: disable=broad-except
       cpu = {"value": None, "unit": "queries/s", "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
   bq = algorithmic_bytes_per_query(counts["evals"], counts["expansions"], counts["sweeps"], d, opt["max_m"],
-                                   opt["max_m0"], topk)
+                                   opt["max_m0"], topk, 2 if args.row_dtype == "f16" else 4)
   achieved = bq * nq / (ms_dev / args.steps * 1e-3) / 1e9
   # DRAM bytes of one launch from the committed ncu capture of this exact workload (dram__bytes_read.sum +
   # dram__bytes_write.sum, profiles/knn_search_kernel_angular_full.md); null for any other shape
   traffic = NCU_TRAFFIC_BYTES if (args.workload == HEADLINE and args.n is None and args.nq is None and
-                                  ef == 300) else None
+                                  ef == 300 and args.row_dtype == "f32") else None
   line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                       "traffic": traffic, "algorithmic_bytes_per_launch": bq * nq, "peak_source": peak_kind,
                       "bytes_per_query": bq, "counts": counts}

@@ -71,6 +71,7 @@ EXTENSIONS = {
   "device_id": (int, -1),
   "search_team": (int, -1),
   "search_schedule": (bool, True),
+  "row_dtype": (str, "f32"),
 }
 ALIASES = {"heuristic_coff": "heuristic_coef"}
 

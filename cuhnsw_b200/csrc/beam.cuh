@@ -15,8 +15,14 @@
 #pragma once
 #include "common.cuh"
 #include "distance.cuh"
+#include "kernels.h"
 
 namespace hnsw {
+
+__device__ __forceinline__ VecTable make_table(const GraphView& g) {
+  return VecTable{static_cast<const unsigned char*>(g.vec), (size_t)g.vstride * (g.f16 ? 2 : 4), (g.d + 3) / 4, g.d,
+                  g.dist_type};
+}
 
 struct WalkCounters {  // per warp and launch
   unsigned evals;       // rows gathered for a distance

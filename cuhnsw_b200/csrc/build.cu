@@ -113,7 +113,7 @@ template <class Dist>
 __device__ __forceinline__ void bind_warp(unsigned char* smem, int per_warp, const GraphView& g, int cap, int vsize,
                                           Dist& de, WarpList& wl, SelBuf& sel) {
   unsigned char* mine = smem + (size_t)(threadIdx.x >> 5) * per_warp;
-  VecTable tab{reinterpret_cast<const float4*>(g.vec), g.vstride / 4, (g.d + 3) / 4, g.d, g.dist_type};
+  const VecTable tab = make_table(g);
   de.init(tab, mine);
   mine += Dist::smem_bytes(g.d);
   wl.bind(mine, cap, vsize, g.n);
@@ -465,28 +465,40 @@ static cudaError_t build_batch_t(const BuildLevel& L, const BuildScratch& S, lon
   return cudaSuccess;
 }
 
-#define HNSW_DISPATCH(d, CALL)                                   \
-  do {                                                           \
-    if ((d) <= 32) return CALL(DistSmall<1>);                    \
-    if ((d) <= 64) return CALL(DistSmall<2>);                    \
-    if ((d) <= 96) return CALL(DistSmall<3>);                    \
-    if ((d) <= 128) return CALL(DistSmall<4>);                   \
-    return CALL(DistLarge);                                      \
+#define HNSW_DISPATCH_ROWS(E, d, CALL)           \
+  do {                                            \
+    if ((d) <= 32) return CALL(typename E::D32);   \
+    if ((d) <= 64) return CALL(typename E::D64);   \
+    if ((d) <= 96) return CALL(typename E::D96);   \
+    if ((d) <= 128) return CALL(typename E::D128); \
+    return CALL(typename E::Wide);                 \
   } while (0)
+
+template <class Row>
+static cudaError_t init_level_rows(const BuildLevel& L, unsigned long long* ticket, int sm_count, cudaStream_t stream) {
+#define CALL(D) init_level_t<D>(L, ticket, sm_count, stream)
+  HNSW_DISPATCH_ROWS(Pick<Row>, L.g.d, CALL);
+#undef CALL
+}
+template <class Row>
+static cudaError_t build_batch_rows(const BuildLevel& L, const BuildScratch& S, long long first, int count,
+                                    int sm_count, cudaStream_t stream) {
+#define CALL(D) build_batch_t<D>(L, S, first, count, sm_count, stream)
+  HNSW_DISPATCH_ROWS(Pick<Row>, L.g.d, CALL);
+#undef CALL
+}
 
 cudaError_t launch_init_level(const BuildLevel& L, unsigned long long* ticket, int sm_count, cudaStream_t stream) {
   if (L.n_level <= 0) return cudaSuccess;
-#define CALL(D) init_level_t<D>(L, ticket, sm_count, stream)
-  HNSW_DISPATCH(L.g.d, CALL);
-#undef CALL
+  return L.g.f16 ? init_level_rows<RowF16>(L, ticket, sm_count, stream)
+                 : init_level_rows<RowF32>(L, ticket, sm_count, stream);
 }
 
 cudaError_t launch_build_batch(const BuildLevel& L, const BuildScratch& S, long long first, int count,
                                int sm_count, cudaStream_t stream) {
   if (count <= 0) return cudaSuccess;
-#define CALL(D) build_batch_t<D>(L, S, first, count, sm_count, stream)
-  HNSW_DISPATCH(L.g.d, CALL);
-#undef CALL
+  return L.g.f16 ? build_batch_rows<RowF16>(L, S, first, count, sm_count, stream)
+                 : build_batch_rows<RowF32>(L, S, first, count, sm_count, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -510,6 +522,26 @@ __global__ void unpad_rows_kernel(const float* src, float* dst, long long n, int
     dst[idx] = src[r * vstride + c];
   }
 }
+// half rows: rounded to nearest even and stored in the paired-column layout of RowF16 (the rows were
+// cleared beforehand, so the padding reads zero)
+__global__ void pad_rows_f16_kernel(const float* src, __half* dst, long long n, int d, int vstride) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long total = n * d;
+  for (; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    long long r = idx / d;
+    int e = (int)(idx % d);
+    dst[r * vstride + RowF16::position(d, e)] = __float2half_rn(src[idx]);
+  }
+}
+__global__ void unpad_rows_f16_kernel(const __half* src, float* dst, long long n, int d, int vstride) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long total = n * d;
+  for (; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    long long r = idx / d;
+    int e = (int)(idx % d);
+    dst[idx] = __half2float(src[r * vstride + RowF16::position(d, e)]);
+  }
+}
 __global__ void fill_i32_kernel(int* p, long long n, int v) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   for (; idx < n; idx += (long long)gridDim.x * blockDim.x) p[idx] = v;
@@ -521,14 +553,25 @@ static unsigned blocks_for(long long total) {
   if (b < 1) b = 1;
   return (unsigned)b;
 }
-cudaError_t launch_pad_rows(const float* src, float* dst, long long n, int d, int vstride, cudaStream_t stream) {
+cudaError_t launch_pad_rows(const float* src, void* dst, long long n, int d, int vstride, int f16,
+                            cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
-  pad_rows_kernel<<<blocks_for(n * vstride), 256, 0, stream>>>(src, dst, n, d, vstride);
+  if (f16) {
+    cudaError_t e = cudaMemsetAsync(dst, 0, (size_t)n * vstride * sizeof(__half), stream);
+    if (e != cudaSuccess) return e;
+    pad_rows_f16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(src, static_cast<__half*>(dst), n, d, vstride);
+  } else {
+    pad_rows_kernel<<<blocks_for(n * vstride), 256, 0, stream>>>(src, static_cast<float*>(dst), n, d, vstride);
+  }
   return cudaGetLastError();
 }
-cudaError_t launch_unpad_rows(const float* src, float* dst, long long n, int d, int vstride, cudaStream_t stream) {
+cudaError_t launch_unpad_rows(const void* src, float* dst, long long n, int d, int vstride, int f16,
+                              cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
-  unpad_rows_kernel<<<blocks_for(n * d), 256, 0, stream>>>(src, dst, n, d, vstride);
+  if (f16)
+    unpad_rows_f16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(static_cast<const __half*>(src), dst, n, d, vstride);
+  else
+    unpad_rows_kernel<<<blocks_for(n * d), 256, 0, stream>>>(static_cast<const float*>(src), dst, n, d, vstride);
   return cudaGetLastError();
 }
 cudaError_t launch_fill_i32(int* p, long long n, int v, cudaStream_t stream) {

@@ -2,7 +2,7 @@
 // primitive (the reference's counterpart is BatchDistanceKernel,
 // cpp/include/cuda_dist_kernels.cuh:143-156).
 #include "kernels.h"
-#include "distance.cuh"
+#include "beam.cuh"
 
 namespace hnsw {
 
@@ -12,7 +12,7 @@ __global__ void __launch_bounds__(64) batch_distance_kernel(GraphView g, const i
   extern __shared__ __align__(16) unsigned char smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   Dist de;
-  VecTable tab{reinterpret_cast<const float4*>(g.vec), g.vstride / 4, (g.d + 3) / 4, g.d, g.dist_type};
+  const VecTable tab = make_table(g);
   de.init(tab, smem + (size_t)warp * Dist::smem_bytes(g.d));
   const long long nwarps = (long long)gridDim.x * 2;
   for (long long base = ((long long)blockIdx.x * 2 + warp) * 32; base < npairs; base += nwarps * 32) {
@@ -40,14 +40,24 @@ static cudaError_t batch_distance_t(const GraphView& g, const int* src, const in
   return cudaGetLastError();
 }
 
+template <class Row>
+static cudaError_t batch_distance_rows(const GraphView& g, const int* src, const int* dst, long long npairs, float* out,
+                                       cudaStream_t stream) {
+  using E = Pick<Row>;
+  if (g.d <= 32) return batch_distance_t<typename E::D32>(g, src, dst, npairs, out, stream);
+  if (g.d <= 64) return batch_distance_t<typename E::D64>(g, src, dst, npairs, out, stream);
+  if (g.d <= 96) return batch_distance_t<typename E::D96>(g, src, dst, npairs, out, stream);
+  if (g.d <= 128) return batch_distance_t<typename E::D128>(g, src, dst, npairs, out, stream);
+  return batch_distance_t<typename E::Wide>(g, src, dst, npairs, out, stream);
+}
+
+int row_stride_elements(int d, int f16) { return f16 ? RowF16::stride(d) : RowF32::stride(d); }
+
 cudaError_t launch_batch_distance(const GraphView& g, const int* src, const int* dst, long long npairs, float* out,
                                   cudaStream_t stream) {
   if (npairs <= 0) return cudaSuccess;
-  if (g.d <= 32) return batch_distance_t<DistSmall<1>>(g, src, dst, npairs, out, stream);
-  if (g.d <= 64) return batch_distance_t<DistSmall<2>>(g, src, dst, npairs, out, stream);
-  if (g.d <= 96) return batch_distance_t<DistSmall<3>>(g, src, dst, npairs, out, stream);
-  if (g.d <= 128) return batch_distance_t<DistSmall<4>>(g, src, dst, npairs, out, stream);
-  return batch_distance_t<DistLarge>(g, src, dst, npairs, out, stream);
+  return g.f16 ? batch_distance_rows<RowF16>(g, src, dst, npairs, out, stream)
+               : batch_distance_rows<RowF32>(g, src, dst, npairs, out, stream);
 }
 
 }  // namespace hnsw

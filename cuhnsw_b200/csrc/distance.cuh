@@ -11,21 +11,75 @@
 //   offsets T/2..1.  DOT returns -sum, L2 the squared distance
 //   (cuda_dist_kernels.cuh:112-124).
 //
-// Rows are stored padded with zeros to a multiple of 8 floats (32-byte sectors).
+// fp32 rows are stored in element order, padded with zeros to a multiple of 8 floats (32-byte sectors).
+//
+// fp16 rows (IEEE half, round to nearest even of the input) keep the same lanes, accumulators and order of
+// additions, so they give exactly the canonical fp32 distance over the rounded values; only the layout
+// differs, so that a lane still loads 16 bytes at a time: a chunk is four consecutive elements, a lane owns
+// chunk columns c = 0, 1, 2, ... (chunk number lane + T*c), and the 8 halves of its columns 2p and 2p + 1
+// are stored side by side at 16-byte slot p*T + lane of the row.  Rows are padded with zeros to whole pairs
+// of columns (T*16 bytes).
 #pragma once
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace hnsw {
 
 struct VecTable {
-  const float4* vec;  // n rows
-  int stride4;        // row stride in float4 units
-  int nchunk;         // ceil(d / 4): chunks that hold data
+  const unsigned char* vec;  // n rows
+  size_t row_bytes;          // row stride
+  int nchunk;                // ceil(d / 4): chunks that hold data
   int d;
   int dist_type;
 };
 
-__device__ __forceinline__ float4 ldg4(const float4* p) { return __ldg(p); }
+// Storage types of a row.  load<N, T>(row, lane, c0, nchunk, v): chunk columns c0 .. c0 + N - 1 of team
+// lane `lane` (team of T lanes) as floats in v[0 .. N - 1]; columns past the end of the row read zeros.
+// kInner: the caller knows that only column c0 + N - 1 can reach past the end.
+struct RowF32 {
+  // elements per row for d dimensions
+  __host__ __device__ static int stride(int d) { return (d + 7) / 8 * 8; }
+  template <int N, int T, bool kInner = false>
+  static __device__ __forceinline__ void load(const unsigned char* row, int lane, int c0, int nchunk, float4* v) {
+#pragma unroll
+    for (int cc = 0; cc < N; ++cc) {
+      const int ch = lane + T * (c0 + cc);
+      v[cc] = ((kInner && cc < N - 1) || ch < nchunk) ? __ldg(reinterpret_cast<const float4*>(row) + ch)
+                                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+};
+struct RowF16 {
+  __host__ __device__ static int team(int d) { return d <= 128 ? 8 : 32; }
+  __host__ __device__ static int stride(int d) {
+    const int t = team(d), nchunk = (d + 3) / 4;
+    return (nchunk + 2 * t - 1) / (2 * t) * t * 8;  // pairs of columns x T slots x 8 halves
+  }
+  // position (in halves) of element e of a row
+  __host__ __device__ static int position(int d, int e) {
+    const int t = team(d), ch = e >> 2, c = ch / t, lane = ch % t;
+    return ((c >> 1) * t + lane) * 8 + (c & 1) * 4 + (e & 3);
+  }
+  template <int N, int T, bool kInner = false>
+  static __device__ __forceinline__ void load(const unsigned char* row, int lane, int c0, int nchunk, float4* v) {
+    const int npair = (nchunk + 2 * T - 1) / (2 * T);
+#pragma unroll
+    for (int jj = 0; jj < (N + 1) / 2; ++jj) {  // c0 is even
+      const int p = (c0 >> 1) + jj;
+      uint4 u = make_uint4(0u, 0u, 0u, 0u);
+      if (kInner || p < npair) u = __ldg(reinterpret_cast<const uint4*>(row) + p * T + lane);
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+      v[2 * jj] = make_float4(a.x, a.y, b.x, b.y);
+      if (2 * jj + 1 < N) {
+        const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&u.z));
+        const float2 e = __half22float2(*reinterpret_cast<const __half2*>(&u.w));
+        v[2 * jj + 1] = make_float4(c.x, c.y, e.x, e.y);
+      }
+    }
+  }
+};
 
 __device__ __forceinline__ void fma4(float4& acc, const float4& a, const float4& b, int dist_type) {
   if (dist_type == DIST_DOT) {
@@ -48,7 +102,7 @@ __device__ __forceinline__ float fold4(const float4& a) { return (a.x + a.y) + (
 // d <= 128: teams of 8 lanes, four rows per warp pass, query chunks in registers.
 // C = ceil(d / 32) chunks per lane.
 // ---------------------------------------------------------------------------
-template <int C>
+template <int C, class Row = RowF32>
 struct DistSmall {
   static constexpr int kTeam = 8;
   static constexpr int kRowsPerPass = 4;
@@ -89,13 +143,7 @@ struct DistSmall {
   }
   // query = stored (padded) row `id`
   __device__ __forceinline__ void load_query_row(int id) {
-    const int tl = lane_id() & 7;
-    const float4* row = t.vec + (size_t)id * t.stride4;
-#pragma unroll
-    for (int c = 0; c < C; ++c) {
-      int ch = tl + 8 * c;
-      q[c] = (ch < t.nchunk) ? ldg4(row + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
+    Row::template load<C, 8>(t.vec + (size_t)id * t.row_bytes, lane_id() & 7, 0, t.nchunk, q);
   }
 
   // Lane r (r < n <= 32, n >= 1) holds a row id; returns the distance to it in lane r.
@@ -115,13 +163,8 @@ struct DistSmall {
         // rows past n are folded onto row 0 of the list: a harmless repeated load whose result nobody selects
         const int r = r0 + 4 * u + team;
         const int rid = __shfl_sync(FULL, id, r < n ? r : 0);
-        const float4* row = t.vec + (size_t)rid * t.stride4;
-#pragma unroll
-        for (int c = 0; c < C; ++c) {
-          const int ch = tl + 8 * c;
-          // only the last chunk column can lie past the end of the row
-          v[u][c] = (c < C - 1 || ch < t.nchunk) ? ldg4(row + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+        // only the last chunk column can lie past the end of the row
+        Row::template load<C, 8, true>(t.vec + (size_t)rid * t.row_bytes, tl, 0, t.nchunk, v[u]);
       }
 #pragma unroll
       for (int u = 0; u < kBatch; ++u) {
@@ -150,7 +193,7 @@ struct DistSmall {
 // the search kernel is compiled for.  <4, 8> (16 float4 in flight, ~125 registers) suits large batches;
 // <8, 4> (32 float4 in flight) is 23 % faster on 1000 queries of d = 960, where resident warps do not
 // matter because there are fewer queries than warp slots.
-template <int kChunksT, int kMinCtasT>
+template <int kChunksT, int kMinCtasT, class Row = RowF32>
 struct DistLargeT {
   static constexpr int kRows = 4;             // rows whose loads are in flight together
   static constexpr int kChunks = kChunksT;    // chunk columns per row per step
@@ -174,9 +217,13 @@ struct DistLargeT {
     __syncwarp();
   }
   __device__ __forceinline__ void load_query_row(int id) {
-    const float4* row = t.vec + (size_t)id * t.stride4;
-    for (int ch = lane_id(); ch < C * 32; ch += 32)
-      sq[ch] = (ch < t.nchunk) ? ldg4(row + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const unsigned char* row = t.vec + (size_t)id * t.row_bytes;
+    for (int c0 = 0; c0 < C; c0 += 2) {
+      float4 v[2];
+      Row::template load<2, 32>(row, lane_id(), c0, t.nchunk, v);
+      sq[lane_id() + 32 * c0] = v[0];
+      if (c0 + 1 < C) sq[lane_id() + 32 * (c0 + 1)] = v[1];
+    }
     __syncwarp();
   }
   __device__ __forceinline__ float eval(int id, int n) {
@@ -195,12 +242,9 @@ struct DistLargeT {
         float4 v[kRows][kChunks];
 #pragma unroll
         for (int u = 0; u < kRows; ++u) {
-          const float4* row = t.vec + (size_t)(rid[u] >= 0 ? rid[u] : 0) * t.stride4;
-#pragma unroll
-          for (int cc = 0; cc < kChunks; ++cc) {
-            int ch = lane + 32 * (c0 + cc);
-            v[u][cc] = (rid[u] >= 0 && ch < t.nchunk) ? ldg4(row + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
+          // rows past n are folded onto row 0: a harmless repeated load whose result nobody selects
+          Row::template load<kChunks, 32>(t.vec + (size_t)(rid[u] >= 0 ? rid[u] : 0) * t.row_bytes, lane, c0, t.nchunk,
+                                          v[u]);
         }
 #pragma unroll
         for (int cc = 0; cc < kChunks; ++cc) {
@@ -229,5 +273,16 @@ struct DistLargeT {
 
 using DistLarge = DistLargeT<4, 8>;      // default: build kernels, large query batches
 using DistLargeDeep = DistLargeT<8, 4>;  // few queries: more loads in flight per warp
+
+// Engines by row width (floats) and storage type: Pick<Row>::D32 ... ::Wide, ::WideDeep
+template <class Row>
+struct Pick {
+  using D32 = DistSmall<1, Row>;
+  using D64 = DistSmall<2, Row>;
+  using D96 = DistSmall<3, Row>;
+  using D128 = DistSmall<4, Row>;
+  using Wide = DistLargeT<4, 8, Row>;
+  using WideDeep = DistLargeT<8, 4, Row>;
+};
 
 }  // namespace hnsw

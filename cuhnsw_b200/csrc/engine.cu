@@ -128,6 +128,8 @@ int Engine::Init(const char* opt_path) {
   o.reverse_cand = js.boolean("reverse_cand", o.reverse_cand);
   o.search_team = (int)js.number("search_team", o.search_team);
   o.search_schedule = js.boolean("search_schedule", o.search_schedule);
+  o.row_dtype = js.string("row_dtype", o.row_dtype);
+  if (o.row_dtype != "f32" && o.row_dtype != "f16") return Fail(kInvalidArgument, "row_dtype must be f32 or f16");
   // the reference's schema spells it heuristic_coef, its README heuristic_coff
   o.heuristic_coef = js.number("heuristic_coef", js.number("heuristic_coff", o.heuristic_coef));
   o.batch_max = (long long)js.number("batch_max", (double)o.batch_max);
@@ -173,11 +175,12 @@ int Engine::SetData(const float* data, long long num_data, int num_dims) {
   if (rc) return rc;
   n_ = num_data;
   d_ = num_dims;
-  vstride_ = round_up(num_dims, 8);
+  f16_ = opt_.row_dtype == "f16";
+  vstride_ = row_stride_elements(num_dims, f16_ ? 1 : 0);  // rows start on 32-byte sectors
   has_levels_ = has_graph_ = labelled_ = false;
   labels_h_.clear();
   labels_d_.release();
-  CU(vec_.alloc((size_t)n_ * vstride_));
+  CU(vec_.alloc(((size_t)n_ * vstride_ * (f16_ ? 2 : 4) + 3) / 4));
   // stage through a bounded device buffer and pad rows on the device
   const long long rows_per_chunk = std::max<long long>(1, (64ll << 20) / num_dims);
   DevBuf<float> raw;
@@ -186,11 +189,11 @@ int Engine::SetData(const float* data, long long num_data, int num_dims) {
     long long r = std::min(rows_per_chunk, n_ - s);
     CU(cudaMemcpyAsync(raw.get(), data + (size_t)s * num_dims, (size_t)r * num_dims * sizeof(float),
                        cudaMemcpyHostToDevice, stream_));
-    CU(launch_pad_rows(raw.get(), vec_.get() + (size_t)s * vstride_, r, num_dims, vstride_, stream_));
+    CU(launch_pad_rows(raw.get(), RowPtr(s), r, num_dims, vstride_, f16_ ? 1 : 0, stream_));
     CU(cudaStreamSynchronize(stream_));
   }
   has_data_ = true;
-  Log(3, "copied data (%lld x %d), row stride %d floats", n_, d_, vstride_);
+  Log(3, "copied data (%lld x %d), row stride %d %s", n_, d_, vstride_, f16_ ? "halves" : "floats");
   return kOk;
 }
 
@@ -249,6 +252,7 @@ GraphView Engine::View() const {
   GraphView g;
   g.vec = vec_.get();
   g.vstride = vstride_;
+  g.f16 = f16_ ? 1 : 0;
   g.d = d_;
   g.dist_type = dist_type_;
   g.n = n_;
@@ -626,14 +630,17 @@ int Engine::SaveIndex(const char* path) {
   // level-0 records, in chunks of rows
   const long long chunk = std::max<long long>(1, (32ll << 20) / (long long)rec);
   std::vector<int> rows((size_t)std::min(chunk, std::max<long long>(n_, 1)) * stride0_);
-  std::vector<float> vecs((size_t)std::min(chunk, std::max<long long>(n_, 1)) * vstride_);
+  std::vector<float> vecs((size_t)std::min(chunk, std::max<long long>(n_, 1)) * d_);
+  DevBuf<float> unpadded;  // the file holds fp32 rows without padding, whatever the storage type
+  CU(unpadded.alloc(vecs.size()));
   std::vector<unsigned char> out((size_t)std::min(chunk, std::max<long long>(n_, 1)) * rec);
   for (long long s = 0; s < n_ && ok; s += chunk) {
     const long long r = std::min(chunk, n_ - s);
     CU(cudaMemcpy(rows.data(), rows0_.get() + (size_t)s * stride0_, (size_t)r * stride0_ * sizeof(int),
                   cudaMemcpyDeviceToHost));
-    CU(cudaMemcpy(vecs.data(), vec_.get() + (size_t)s * vstride_, (size_t)r * vstride_ * sizeof(float),
-                  cudaMemcpyDeviceToHost));
+    CU(launch_unpad_rows(RowPtr(s), unpadded.get(), r, d_, vstride_, f16_ ? 1 : 0, stream_));
+    CU(cudaMemcpyAsync(vecs.data(), unpadded.get(), (size_t)r * d_ * sizeof(float), cudaMemcpyDeviceToHost, stream_));
+    CU(cudaStreamSynchronize(stream_));
     std::memset(out.data(), 0, (size_t)r * rec);
     for (long long i = 0; i < r; ++i) {
       unsigned char* o = out.data() + (size_t)i * rec;
@@ -646,7 +653,7 @@ int Engine::SaveIndex(const char* path) {
           ++deg;
         }
       std::memcpy(o, &deg, 4);
-      std::memcpy(o + 4 + 4 * (size_t)m0, vecs.data() + (size_t)i * vstride_, 4 * (size_t)d_);
+      std::memcpy(o + 4 + 4 * (size_t)m0, vecs.data() + (size_t)i * d_, 4 * (size_t)d_);
       uint64_t label = labelled_ ? (uint64_t)labels_h_[(size_t)(s + i)] : (uint64_t)(s + i);
       std::memcpy(o + rec - 8, &label, 8);
     }

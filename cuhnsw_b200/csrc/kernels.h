@@ -8,8 +8,10 @@ namespace hnsw {
 
 // Device-resident index.  All ids are global node ids on every layer.
 struct GraphView {
-  const float* vec;       // n x vstride, rows zero padded, 32-byte aligned rows
-  int vstride;            // floats per row (multiple of 8)
+  const void* vec;        // n x vstride elements, rows zero padded, 32-byte aligned rows
+  int vstride;            // elements per row (row_stride_elements)
+  int f16;                // rows are stored as IEEE half (round to nearest even of the input); distances are
+                          // the fp32 distances over the stored values
   int d;
   int dist_type;          // 0 dot (-dot), 1 l2 (squared)
   long long n;
@@ -122,9 +124,13 @@ cudaError_t launch_init_level(const BuildLevel& L, unsigned long long* ticket, i
 // one insertion batch: nodes [first, first + count) of the level's node list
 cudaError_t launch_build_batch(const BuildLevel& L, const BuildScratch& S, long long first, int count,
                                int sm_count, cudaStream_t stream);
-// pads an unpadded n x d matrix into n x vstride rows
-cudaError_t launch_pad_rows(const float* src, float* dst, long long n, int d, int vstride, cudaStream_t stream);
-cudaError_t launch_unpad_rows(const float* src, float* dst, long long n, int d, int vstride, cudaStream_t stream);
+// elements per stored row: d rounded up to 8 floats, or whole pairs of chunk columns of halves
+int row_stride_elements(int d, int f16);
+// pads an unpadded n x d fp32 matrix into n x vstride rows of floats or halves, and back
+cudaError_t launch_pad_rows(const float* src, void* dst, long long n, int d, int vstride, int f16,
+                            cudaStream_t stream);
+cudaError_t launch_unpad_rows(const void* src, float* dst, long long n, int d, int vstride, int f16,
+                              cudaStream_t stream);
 cudaError_t launch_fill_i32(int* p, long long n, int v, cudaStream_t stream);
 // merges parts x nq x k per-shard rows (global ids, -1 = empty) into nq x k rows ordered by (distance, id)
 cudaError_t launch_merge_topk(const int* ids, const float* dist, int parts, long long nq, int k, int* out_ids,

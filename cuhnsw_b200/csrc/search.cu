@@ -21,7 +21,7 @@ knn_search_kernel(SearchParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned char* mine = smem + (size_t)warp * p.smem_per_warp;
   Dist de;
-  VecTable tab{reinterpret_cast<const float4*>(p.g.vec), p.g.vstride / 4, (p.g.d + 3) / 4, p.g.d, p.g.dist_type};
+  const VecTable tab = make_table(p.g);
   de.init(tab, mine);
   WarpList wl;
   wl.bind(mine + Dist::smem_bytes(p.g.d), p.ef, p.vsize, p.g.n);
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) entry_kernel(SearchParams p
   const long long qi = (long long)blockIdx.x * kWarpsPerCta + warp;
   if (qi >= p.nq) return;
   Dist de;
-  VecTable tab{reinterpret_cast<const float4*>(p.g.vec), p.g.vstride / 4, (p.g.d + 3) / 4, p.g.d, p.g.dist_type};
+  const VecTable tab = make_table(p.g);
   de.init(tab, smem + (size_t)warp * Dist::smem_bytes(p.g.d));
   WalkCounters wc{0, 0, 0, 0};
   de.load_query(p.queries + (size_t)qi * p.g.d);
@@ -120,6 +120,17 @@ static cudaError_t launch_entry_t(const SearchParams& p, const SearchSchedule& s
   return cudaGetLastError();
 }
 
+template <class Row>
+static cudaError_t launch_entry_rows(const SearchParams& p, const SearchSchedule& s, cudaStream_t stream) {
+  using E = Pick<Row>;
+  const int d = p.g.d;
+  return d <= 32    ? launch_entry_t<typename E::D32>(p, s, stream)
+         : d <= 64  ? launch_entry_t<typename E::D64>(p, s, stream)
+         : d <= 96  ? launch_entry_t<typename E::D96>(p, s, stream)
+         : d <= 128 ? launch_entry_t<typename E::D128>(p, s, stream)
+                    : launch_entry_t<typename E::Wide>(p, s, stream);
+}
+
 size_t search_schedule_tmp_bytes(long long nq) {
   size_t bytes = 0;
   cub::DeviceRadixSort::SortPairs(nullptr, bytes, (const unsigned*)nullptr, (unsigned*)nullptr, (const int*)nullptr,
@@ -130,12 +141,7 @@ size_t search_schedule_tmp_bytes(long long nq) {
 cudaError_t schedule_search(SearchParams& p, const SearchSchedule& s, int sm_count, cudaStream_t stream) {
   (void)sm_count;
   if (p.nq > s.capacity) return cudaErrorInvalidValue;
-  const int d = p.g.d;
-  cudaError_t e = d <= 32    ? launch_entry_t<DistSmall<1>>(p, s, stream)
-                  : d <= 64  ? launch_entry_t<DistSmall<2>>(p, s, stream)
-                  : d <= 96  ? launch_entry_t<DistSmall<3>>(p, s, stream)
-                  : d <= 128 ? launch_entry_t<DistSmall<4>>(p, s, stream)
-                             : launch_entry_t<DistLarge>(p, s, stream);
+  cudaError_t e = p.g.f16 ? launch_entry_rows<RowF16>(p, s, stream) : launch_entry_rows<RowF32>(p, s, stream);
   if (e != cudaSuccess) return e;
   // the upper 16 bits of the key (sign, exponent, 7 bits of mantissa) order the queries finely enough
   size_t bytes = s.sort_tmp_bytes;
@@ -207,19 +213,27 @@ int search_kernel_kind(int d, long long nq, int team, int reverse_cand, int sm_c
   return kSearchWarp;
 }
 
-cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream, const SearchSchedule* sched) {
-  if (p.nq <= 0) return cudaSuccess;
+template <class Row>
+static cudaError_t launch_search_rows(const SearchParams& p, int sm_count, cudaStream_t stream,
+                                      const SearchSchedule* sched) {
+  using E = Pick<Row>;
   const int d = p.g.d;
-  if (d <= 32) return launch_search_t<DistSmall<1>>(p, sm_count, stream, sched);
-  if (d <= 64) return launch_search_t<DistSmall<2>>(p, sm_count, stream, sched);
-  if (d <= 96) return launch_search_t<DistSmall<3>>(p, sm_count, stream, sched);
-  if (d <= 128) return launch_search_t<DistSmall<4>>(p, sm_count, stream, sched);
+  if (d <= 32) return launch_search_t<typename E::D32>(p, sm_count, stream, sched);
+  if (d <= 64) return launch_search_t<typename E::D64>(p, sm_count, stream, sched);
+  if (d <= 96) return launch_search_t<typename E::D96>(p, sm_count, stream, sched);
+  if (d <= 128) return launch_search_t<typename E::D128>(p, sm_count, stream, sched);
   switch (search_kernel_kind(d, p.nq, p.team, p.reverse_cand, sm_count)) {
     case kSearchTeam: return launch_search_team(p, sm_count, stream, sched);
-    case kSearchWarpDeep: return launch_search_t<DistLargeDeep>(p, sm_count, stream, sched);
+    case kSearchWarpDeep: return launch_search_t<typename E::WideDeep>(p, sm_count, stream, sched);
     default: break;
   }
-  return launch_search_t<DistLarge>(p, sm_count, stream, sched);
+  return launch_search_t<typename E::Wide>(p, sm_count, stream, sched);
+}
+
+cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream, const SearchSchedule* sched) {
+  if (p.nq <= 0) return cudaSuccess;
+  return p.g.f16 ? launch_search_rows<RowF16>(p, sm_count, stream, sched)
+                 : launch_search_rows<RowF32>(p, sm_count, stream, sched);
 }
 
 }  // namespace hnsw

@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(kTeamWarps * 32, 4) knn_search_team_kernel(Sea
   const size_t qbytes = Base::smem_bytes(p.g.d);
   TeamMailbox* mb = reinterpret_cast<TeamMailbox*>(smem + qbytes);
   unsigned char* list_mem = smem + qbytes + sizeof(TeamMailbox);
-  VecTable tab{reinterpret_cast<const float4*>(p.g.vec), p.g.vstride / 4, (p.g.d + 3) / 4, p.g.d, p.g.dist_type};
+  const VecTable tab = make_table(p.g);
   Base base;
   base.init(tab, smem);  // every warp reads the one query copy in shared memory
 
@@ -134,7 +134,7 @@ cudaError_t launch_search_team(const SearchParams& p0, int sm_count, cudaStream_
   SearchParams p = p0;
   const size_t smem = search_team_smem(p.g.d, p.ef, p.vsize, p.g.n);
   p.smem_per_warp = (int)smem;
-  auto kern = knn_search_team_kernel<DistLarge>;
+  auto kern = p.g.f16 ? knn_search_team_kernel<Pick<RowF16>::Wide> : knn_search_team_kernel<Pick<RowF32>::Wide>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   int per_sm = 0;

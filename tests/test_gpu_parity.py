@@ -319,6 +319,66 @@ def test_degenerate_builds():
   assert (dist == 0).all() and (ids == oracle.search(g, base[:4], 10, 50)[0]).all()
 
 
+# ---------------------------------------------------------------- fp16 rows
+def _rounded(x):
+  return x.astype(np.float16).astype(np.float32)
+
+
+@pytest.mark.parametrize("d,dist_type", [(50, "dot"), (33, "l2"), (128, "l2"), (200, "dot"), (960, "l2")])
+def test_half_rows_give_the_canonical_distance_over_the_rounded_values(d, dist_type, tmp_path):
+  """row_dtype = f16 stores round-to-nearest-even halves; every distance, and therefore every search and
+  every built graph, equals the fp32 oracle run on the rounded vectors, bit for bit."""
+  rng = np.random.default_rng(77 + d)
+  n = 3000
+  base = (rng.standard_normal((n, d)) * (3.0 if dist_type == "l2" else 1.0)).astype(np.float32)
+  q = rng.standard_normal((150, d)).astype(np.float32)
+  base_r = _rounded(base)
+  opt = {"dist_type": dist_type, "max_m": 12, "max_m0": 24, "ef_construction": 80, "level_mult": 0.4, "seed": 9,
+         "row_dtype": "f16", "batch_max": 300}
+  eng = CuHNSW(engine_options(opt))
+  eng.set_data(base)
+  src = rng.integers(0, n, 500).astype(np.int32)
+  dst = rng.integers(0, n, 500).astype(np.int32)
+  got = eng.obj.batch_distance(src, dst)
+  want = np.array([oracle.distance(base_r[a], base_r[b], dist_type) for a, b in zip(src, dst)], np.float32)
+  assert_same_bits(got, want)
+  # build: same graph as the oracle on the rounded rows with the same batch schedule
+  eng.build()
+  levels, rows0, rows_u = eng.obj.get_graph()
+  g = oracle.build_graph(base_r, levels, 12, 24, dist_type, 80, bmax=300)
+  assert (rows0 == g.rows0).all() and (rows_u[:g.rowsU.shape[0]] == g.rowsU).all()
+  # search: fp32 queries against half rows
+  for ef in (10, 100):
+    ids, dist, found = eng.search_knn(q, 10, ef)
+    oids, odist, ofound = oracle.search(g, q, 10, ef)
+    assert (ids == oids).all() and (found == ofound).all()
+    assert_same_bits(dist, odist)
+  # the file holds the rounded values as fp32; loading it into half rows loses nothing
+  p1, p2 = str(tmp_path / "h1.index"), str(tmp_path / "h2.index")
+  eng.save_index(p1)
+  assert (index_file.load(p1, dist_type).vec == base_r).all()
+  eng2 = CuHNSW(engine_options({"dist_type": dist_type, "row_dtype": "f16"}))
+  eng2.load_index(p1)
+  eng2.save_index(p2)
+  assert open(p1, "rb").read() == open(p2, "rb").read()
+  a, b = eng.search_knn(q, 10, 50), eng2.search_knn(q, 10, 50)
+  assert all((x == y).all() for x, y in zip(a, b))
+
+
+def test_half_rows_keep_recall():
+  base, q, opt = small_workload("angular_full", 50000, 500)
+  truth = ds.ground_truth(base, q, 10, opt["dist_type"])
+  rec = {}
+  for dt in ("f32", "f16"):
+    eng = CuHNSW(engine_options(opt, row_dtype=dt))
+    eng.set_data(base)
+    eng.build()
+    rec[dt] = ds.recall(eng.search_knn(q, 10, 200)[0], truth)
+  assert rec["f16"] >= rec["f32"] - 0.01, rec
+  with pytest.raises(RuntimeError, match="row_dtype"):
+    CuHNSW(engine_options(opt, row_dtype="bf16"))
+
+
 # ---------------------------------------------------------------- index file
 def test_save_load_save_is_byte_identical_and_oracle_readable(tmp_path):
   base, q, opt = small_workload("angular_toy", 5000, 100)

@@ -116,8 +116,10 @@ struct DistSmall {
 #ifndef HNSW_SEARCH_MIN_CTAS
 #define HNSW_SEARCH_MIN_CTAS 16
 #endif
+  // construction: 16 CTAs (64 registers) measured 6 % faster than 12 for rows of up to 64 floats
+  // (1.18 M x 50: 0.208 s against 0.222 s); wider rows keep their query and a row pass in more registers
 #ifndef HNSW_BUILD_MIN_CTAS
-#define HNSW_BUILD_MIN_CTAS 12
+#define HNSW_BUILD_MIN_CTAS (C <= 2 ? 16 : 12)
 #endif
   static constexpr int kSearchMinCtas = HNSW_SEARCH_MIN_CTAS;
   static constexpr int kBuildMinCtas = HNSW_BUILD_MIN_CTAS;

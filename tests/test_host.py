@@ -131,6 +131,22 @@ def test_option_schema_matches_config_proto():
   assert aux.load_json_string('{"a": 1, // c\n "b": [1, 2,],}') == {"a": 1, "b": [1, 2]}
 
 
+def test_extension_options_and_their_validation():
+  """Keys this engine adds to the reference's schema: defaults, types, and what the C++ side refuses."""
+  proto = aux.get_opt_as_proto({})
+  assert (proto.batch_max, proto.ramp_div, proto.device_id) == (0, 16, -1)
+  assert (proto.search_team, proto.search_schedule, proto.row_dtype) == (-1, True, "f32")
+  d = aux.proto_to_dict(aux.get_opt_as_proto({"row_dtype": "f16", "search_schedule": False, "search_team": 1}))
+  assert d["row_dtype"] == "f16" and d["search_schedule"] is False and d["search_team"] == 1
+  with pytest.raises(TypeError):
+    aux.get_opt_as_proto({"row_dtype": 16})
+  with tempfile.TemporaryDirectory() as tmp:
+    b = CuHNSWBind()
+    assert b.init(write_opt(tmp, {"row_dtype": "f16", "search_schedule": False}))
+    with pytest.raises(RuntimeError, match="row_dtype must be f32 or f16"):
+      CuHNSWBind().init(write_opt(tmp, {"row_dtype": "bf16"}))
+
+
 def test_python_api_constructor_semantics():
   from cuhnsw_b200 import CuHNSW
   c = CuHNSW({"py_log_level": 1, "c_log_level": 0})
@@ -147,6 +163,7 @@ def test_python_api_constructor_semantics():
 def test_benchmark_arithmetic():
   import bench
   assert bench.algorithmic_bytes_per_query(10, 2, 1, 50, 12, 24, 10) == 10 * 200 + 2 * 100 + 52 + 200 + 80
+  assert bench.algorithmic_bytes_per_query(10, 2, 1, 50, 12, 24, 10, 2) == 10 * 100 + 2 * 100 + 52 + 200 + 80
   assert bench.pick_ef({50: 0.9, 100: 0.96, 300: 0.99}) == 100
   assert bench.pick_ef({50: 0.5, 100: 0.6}) == 100
   peak, kind = bench.measured_peak()

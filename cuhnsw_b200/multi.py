@@ -72,13 +72,16 @@ class ShardedSearcher:
       gids = torch.where(ids >= 0, ids + self.id_offset, ids)
     else:
       gids = np.where(ids >= 0, ids + self.id_offset, ids).astype(np.int32)
-    all_ids = gather_rows(gids, self.world, self.group)
-    all_d = gather_rows(dist, self.world, self.group)
-    if is_tensor and self.device_merge is not None and all_ids[0].is_cuda:
-      return self.device_merge(torch.stack(all_ids), torch.stack(all_d), topk)
-    ids_np = np.stack([t.cpu().numpy() for t in all_ids])
-    d_np = np.stack([t.cpu().numpy() for t in all_d])
-    return merge_topk_host(ids_np, d_np, topk)
+    # one exchange: ids and the bit patterns of the distances travel in the same int32 buffer
+    gt = gids if is_tensor else torch.from_numpy(gids)
+    dt = dist if is_tensor else torch.from_numpy(np.ascontiguousarray(dist, np.float32))
+    packed = torch.stack([gt.to(torch.int32), dt.contiguous().view(torch.int32)])
+    parts = gather_rows(packed, self.world, self.group)
+    all_ids = torch.stack([t[0] for t in parts])
+    all_d = torch.stack([t[1] for t in parts]).view(torch.float32)
+    if is_tensor and self.device_merge is not None and all_ids.is_cuda:
+      return self.device_merge(all_ids, all_d, topk)
+    return merge_topk_host(all_ids.cpu().numpy(), all_d.cpu().numpy(), topk)
 
 
 def device_merge(ids, dist, topk, stream_ptr=0):

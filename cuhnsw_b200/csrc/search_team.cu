@@ -13,7 +13,10 @@
 
 namespace hnsw {
 
-constexpr int kTeamWarps = 4;
+#ifndef HNSW_TEAM_WARPS
+#define HNSW_TEAM_WARPS 4
+#endif
+constexpr int kTeamWarps = HNSW_TEAM_WARPS;
 
 struct TeamMailbox {
   int n;  // rows to evaluate; -1 = the walk is over
@@ -44,7 +47,7 @@ struct DistTeam {
 };
 
 template <class Base>
-__global__ void __launch_bounds__(kTeamWarps * 32, 4) knn_search_team_kernel(SearchParams p) {
+__global__ void __launch_bounds__(kTeamWarps * 32, 16 / kTeamWarps) knn_search_team_kernel(SearchParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t qbytes = Base::smem_bytes(p.g.d);

@@ -9,7 +9,7 @@ oracle/build_ref.sh).  Writes into the directory given as argv[1]:
   ref_built_angular.npz     data, levels, queries and the reference's search results on its own index
   ref_quality.json          recall@10 and seconds of the reference's build on the 100 000-point workload
 
-Run on a GPU machine:  python tests/golden/make_ref_fixtures.py gpurun_out/golden
+Run on a GPU machine:  python tests/golden/make_ref_fixtures.py <output directory>
 """
 import ctypes
 import json

@@ -140,7 +140,7 @@ size_t search_schedule_tmp_bytes(long long nq) {
 
 cudaError_t schedule_search(SearchParams& p, const SearchSchedule& s, int sm_count, cudaStream_t stream) {
   (void)sm_count;
-  if (p.nq > s.capacity) return cudaErrorInvalidValue;
+  if (p.nq > s.capacity || p.nq > 0x7fffffffll) return cudaErrorInvalidValue;  // the sort counts items in an int
   cudaError_t e = p.g.f16 ? launch_entry_rows<RowF16>(p, s, stream) : launch_entry_rows<RowF32>(p, s, stream);
   if (e != cudaSuccess) return e;
   // the upper 16 bits of the key (sign, exponent, 7 bits of mantissa) order the queries finely enough
@@ -185,7 +185,7 @@ static cudaError_t launch_search_tr(const SearchParams& p0, int sm_count, cudaSt
   if (grid > want) grid = want;
   if (grid < 1) grid = 1;
   // more queries than resident warps: start the long walks first
-  if (sched && p.nq > grid * kWarpsPerCta && p.nq <= sched->capacity) {
+  if (sched && p.nq > grid * kWarpsPerCta && p.nq <= sched->capacity && p.nq <= 0x7fffffffll) {
     e = schedule_search(p, *sched, sm_count, stream);
     if (e != cudaSuccess) return e;
   }

@@ -147,7 +147,7 @@ cudaError_t launch_search_team(const SearchParams& p0, int sm_count, cudaStream_
   long long grid = (long long)per_sm * sm_count;
   if (grid > p.nq) grid = p.nq;
   if (grid < 1) grid = 1;
-  if (sched && p.nq > grid && p.nq <= sched->capacity) {  // more queries than resident CTAs: long walks first
+  if (sched && p.nq > grid && p.nq <= sched->capacity && p.nq <= 0x7fffffffll) {  // more queries than resident CTAs: long walks first
     e = schedule_search(p, *sched, sm_count, stream);
     if (e != cudaSuccess) return e;
   }

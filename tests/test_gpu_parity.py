@@ -365,6 +365,33 @@ def test_half_rows_give_the_canonical_distance_over_the_rounded_values(d, dist_t
   assert all((x == y).all() for x, y in zip(a, b))
 
 
+def test_half_rows_degenerate_shapes():
+  """One dimension, one row, empty index, values that overflow or underflow half precision."""
+  rng = np.random.default_rng(3)
+  for n, d in ((1, 1), (5, 3), (40, 17)):
+    base = rng.standard_normal((n, d)).astype(np.float32)
+    base[0, 0] = 1e-6   # subnormal in half
+    if n > 1:
+      base[1, 0] = 7e4  # beyond the largest half: stored as +inf, like numpy's conversion
+    eng = CuHNSW(engine_options({"dist_type": "l2", "row_dtype": "f16", "max_m": 4, "max_m0": 8, "ef_construction": 16}))
+    eng.set_data(base)
+    eng.build()
+    levels, rows0, _ = eng.obj.get_graph()
+    with np.errstate(over="ignore"):
+      g = oracle.build_graph(_rounded(base), levels, 4, 8, "l2", 16, bmax=int(4 * 10 * eng.obj.describe()["sm_count"] * 4))
+      assert (rows0 == g.rows0).all()
+      q = rng.standard_normal((6, d)).astype(np.float32)
+      ids, dist, found = eng.search_knn(q, 4, 16)
+      oids, odist, ofound = oracle.search(g, q, 4, 16)
+    assert (ids == oids).all() and (found == ofound).all()
+    assert_same_bits(dist, odist)
+  empty = CuHNSW(engine_options({"dist_type": "l2", "row_dtype": "f16"}))
+  empty.set_data(np.zeros((0, 8), np.float32))
+  empty.build()
+  ids, dist, found = empty.search_knn(np.zeros((3, 8), np.float32), 5, 10)
+  assert (found == 0).all() and (ids == -1).all()
+
+
 def test_half_rows_keep_recall():
   base, q, opt = small_workload("angular_full", 50000, 500)
   truth = ds.ground_truth(base, q, 10, opt["dist_type"])

@@ -119,9 +119,10 @@ struct DistSmall {
 #define HNSW_SEARCH_MIN_CTAS (C <= 3 ? 16 : 14)
 #endif
   // construction: 16 CTAs (64 registers) measured 6 % faster than 12 for rows of up to 64 floats
-  // (1.18 M x 50: 0.208 s against 0.222 s); wider rows keep their query and a row pass in more registers
+  // (1.18 M x 50: 0.208 s against 0.222 s) and 2.5 % faster for 96 (2 M x 96: 0.310 against 0.318 s);
+  // rows of 128 floats are 15 % slower there (1 M x 128: 0.477 against 0.415 s)
 #ifndef HNSW_BUILD_MIN_CTAS
-#define HNSW_BUILD_MIN_CTAS (C <= 2 ? 16 : 12)
+#define HNSW_BUILD_MIN_CTAS (C <= 3 ? 16 : 12)
 #endif
   static constexpr int kSearchMinCtas = HNSW_SEARCH_MIN_CTAS;
   static constexpr int kBuildMinCtas = HNSW_BUILD_MIN_CTAS;

@@ -39,7 +39,8 @@ sys.path.insert(0, ROOT)
 HEADLINE = "angular_full"
 RECALL_TARGET = 0.95
 FLUSH_BYTES = 256 << 20  # > 126 MB L2
-NCU_TRAFFIC_BYTES = 3.150e9  # knn_search_kernel, per launch of 10 000 queries at ef_search 300, from the ncu capture under profiles/
+# DRAM bytes of one knn_search_kernel launch of 10 000 queries, by ef_search, from the ncu captures under profiles/
+NCU_TRAFFIC_BYTES = {200: 2.565e9, 300: 3.150e9}
 
 
 def parse():
@@ -67,7 +68,14 @@ class ClockSampler:
   def __init__(self, gpu_index):
     self.gpu = gpu_index
     self.proc = None
-    self.lines = []
+    self.lines = []  # (arrival time, line)
+    self.t0 = self.t1 = None
+
+  def window_open(self):
+    self.t0 = time.monotonic()
+
+  def window_close(self):
+    self.t1 = time.monotonic()
 
   def start(self):
     try:
@@ -81,7 +89,7 @@ class ClockSampler:
 
   def _read(self):
     for line in self.proc.stdout:
-      self.lines.append(line.strip())
+      self.lines.append((time.monotonic(), line.strip()))
 
   def stop(self):
     if self.proc is None:
@@ -91,8 +99,15 @@ class ClockSampler:
       self.proc.wait(timeout=5)
     except subprocess.TimeoutExpired:
       self.proc.kill()
+    # nvidia-smi needs a few hundred ms to print its first sample, so it is started well before the timed
+    # region; only the samples that arrived while the region ran are kept
+    lines = [ln for t, ln in self.lines
+             if self.t0 is not None and self.t1 is not None and self.t0 <= t <= self.t1 + 0.03]
+    window = "timed region"
+    if not lines:
+      lines, window = [ln for _, ln in self.lines], "whole run (no sample arrived inside the timed region)"
     sm, mx, reasons = [], [], set()
-    for line in self.lines:
+    for line in lines:
       parts = [p.strip() for p in line.split(",")]
       if len(parts) < 9:
         continue
@@ -105,7 +120,7 @@ class ClockSampler:
         if val.lower().startswith("active"):
           reasons.add(name)
     return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-            "samples": len(sm), "reasons": sorted(reasons)}
+            "samples": len(sm), "window": window, "reasons": sorted(reasons)}
 
 
 def host_threads():
@@ -173,7 +188,7 @@ def run_reference(args, rank, world):
   levels = ds.random_levels(n, opt["seed"], opt["level_mult"])
   t0 = time.perf_counter()
   g = oracle.build_graph(base, levels, opt["max_m"], opt["max_m0"], opt["dist_type"], opt["ef_construction"],
-                         0.25, False, bmax=23680, ramp_div=16, nthreads=threads, native=native)
+                         0.25, False, bmax=23680, ramp_div=4, nthreads=threads, native=native)
   build_s = time.perf_counter() - t0
   sample = queries[:2000]
   truth = ds.ground_truth(base, sample, topk, opt["dist_type"])
@@ -243,6 +258,9 @@ def run_ours(args, rank, world, local_rank):
   engine.build()
   build_s = time.perf_counter() - t0
   engine.obj.set_stream(torch.cuda.current_stream().cuda_stream)
+  sampler = ClockSampler(local_rank)
+  if rank == 0:
+    sampler.start()
 
   # ef_search: smallest value of the sweep that reaches the recall target on this index
   nr = min(nq, args.recall_queries)
@@ -338,14 +356,13 @@ def run_ours(args, rank, world, local_rank):
       dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
 
-  sampler = ClockSampler(local_rank)
-  if rank == 0:
-    sampler.start()
+  sampler.window_open()
   engine.obj.enable_stats(True)
   ms_dev = timed(step_device)
   stats = engine.obj.get_stats()
   engine.obj.enable_stats(False)
   ms_e2e = timed(step_host)
+  sampler.window_close()
   clocks = sampler.stop() if rank == 0 else None
   # sanity of the last timed result: sorted rows, full rows
   assert int(found_pin.min()) == min(topk, n * (world if sharded else 1)), "search returned short rows"
@@ -395,8 +412,8 @@ def run_ours(args, rank, world, local_rank):
   achieved = bq * nq / (ms_dev / args.steps * 1e-3) / 1e9
   # DRAM bytes of one launch from the committed ncu capture of this exact workload (dram__bytes_read.sum +
   # dram__bytes_write.sum, profiles/knn_search_kernel_angular_full.md); null for any other shape
-  traffic = NCU_TRAFFIC_BYTES if (args.workload == HEADLINE and args.n is None and args.nq is None and
-                                  ef == 300 and args.row_dtype == "f32") else None
+  traffic = NCU_TRAFFIC_BYTES.get(ef) if (args.workload == HEADLINE and args.n is None and args.nq is None and
+                                          args.row_dtype == "f32") else None
   line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                       "traffic": traffic, "algorithmic_bytes_per_launch": bq * nq, "peak_source": peak_kind,
                       "bytes_per_query": bq, "counts": counts}

@@ -67,7 +67,7 @@ SCHEMA = {
 # keys this engine adds; optional, never required
 EXTENSIONS = {
   "batch_max": (int, 0),
-  "ramp_div": (int, 16),
+  "ramp_div": (int, 4),
   "device_id": (int, -1),
   "search_team": (int, -1),
   "search_schedule": (bool, True),

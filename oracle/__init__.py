@@ -104,7 +104,7 @@ class Graph:
 
 
 def build_graph(vec, levels, max_m, max_m0, dist_type, ef_construction, heuristic_coef=0.25, save_remains=False,
-                bmax=1, ramp_div=16, nthreads=0, native=False, reverse_cand=False):
+                bmax=1, ramp_div=4, nthreads=0, native=False, reverse_cand=False):
   """Oracle build.  ``bmax=1`` is the strictly sequential reference-semantics
   schedule; any other value mirrors the batch schedule of the CUDA build."""
   g = Graph(vec, levels, max_m, max_m0, dist_type)

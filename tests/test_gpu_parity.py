@@ -247,7 +247,7 @@ def test_built_graph_bit_exact_with_oracle_on_the_same_batch_schedule(name, n, c
   assert (levels == ds.random_levels(n, opt["seed"], opt["level_mult"])).all()
   bmax = batch_max or int(4 * 10 * (info["sm_count"] * 128 // 32))
   g = oracle.build_graph(base, levels, opt["max_m"], opt["max_m0"], opt["dist_type"], opt["ef_construction"], coef,
-                         save_remains, bmax=bmax, ramp_div=16)
+                         save_remains, bmax=bmax, ramp_div=4)
   assert info["max_level"] == g.max_level and info["enter_point"] == g.enter_point
   assert (rows0 == g.rows0).all()
   assert (rows_u[:g.rowsU.shape[0]] == g.rowsU).all()

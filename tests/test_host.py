@@ -134,7 +134,7 @@ def test_option_schema_matches_config_proto():
 def test_extension_options_and_their_validation():
   """Keys this engine adds to the reference's schema: defaults, types, and what the C++ side refuses."""
   proto = aux.get_opt_as_proto({})
-  assert (proto.batch_max, proto.ramp_div, proto.device_id) == (0, 16, -1)
+  assert (proto.batch_max, proto.ramp_div, proto.device_id) == (0, 4, -1)
   assert (proto.search_team, proto.search_schedule, proto.row_dtype) == (-1, True, "f32")
   d = aux.proto_to_dict(aux.get_opt_as_proto({"row_dtype": "f16", "search_schedule": False, "search_team": 1}))
   assert d["row_dtype"] == "f16" and d["search_schedule"] is False and d["search_team"] == 1

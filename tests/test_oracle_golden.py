@@ -93,7 +93,7 @@ def test_oracle_build_quality_not_below_reference_kernels(golden_dir):
   truth = ds.ground_truth(base, q, 10, "dot")
   for bmax in (1, 23680):
     g = oracle.build_graph(base, levels, opt["max_m"], opt["max_m0"], "dot", opt["ef_construction"], 0.25, False,
-                           bmax=bmax, ramp_div=16)
+                           bmax=bmax, ramp_div=4)
     for ef in (50, 100, 300):
       ids, _, _ = oracle.search(g, q, 10, ef)
       assert ds.recall(ids, truth) >= ref["recall_at_10"][str(ef)] - 0.005, (bmax, ef)

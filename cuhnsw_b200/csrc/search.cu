@@ -1,5 +1,7 @@
-// Batch kNN search: greedy descent through the upper layers fused with the
-// ef_search-bounded layer-0 search in ONE launch over a device-resident graph.
+// Batch kNN search over a device-resident graph: greedy descent through the upper layers and the
+// ef_search-bounded layer-0 search in ONE launch (knn_search_kernel), or, for batches that need more
+// than one wave of warps, a descent kernel, a sort of the queries by entry distance and the same search
+// kernel serving the farthest entries first (entry_kernel, schedule_search).
 //
 // Replaces GetEntryPointsKernel + SearchGraphKernel and their host driver
 // (cpp/include/cuda_search_kernels.cuh:11-165, cpp/src/cuhnsw_build.cu:210-290),

@@ -7,6 +7,7 @@ synthetic stand-in of that file, or on a real ann-benchmarks HDF5 file when one 
 h5py is importable.  hnswlib arms run only if hnswlib is importable.
 
   python -m cuhnsw_b200.examples.example1 [--workload angular_toy] [--hdf5 path] [--topk 10] [--ef-search 300]
+                                          [--row-dtype f16]
 """
 import argparse
 import os
@@ -104,8 +105,10 @@ def main():
   ap.add_argument("--ef-search", type=int, default=300)
   ap.add_argument("--large", type=int, default=100000, help="size of the random query batch of the timing run")
   ap.add_argument("--truth-device", default="cuda")
+  ap.add_argument("--row-dtype", default="f32", choices=["f32", "f16"], help="storage type of the rows on the device")
   args = ap.parse_args()
   data, queries, neighbors, opt = load_data(args)
+  opt["row_dtype"] = args.row_dtype
   with tempfile.TemporaryDirectory() as tmp:
     index_path = os.path.join(tmp, "cuhnsw.index")
     run_gpu_training(data, opt, index_path)

@@ -1,7 +1,8 @@
 """Option handling and logging of the Python layer.
 
-Mirrors cuhnsw/aux.py of the reference (get_logger :18-36, Option :79-119,
-get_opt_as_proto :60-67, proto_to_dict :69-72).  The reference validates the
+Same functions as cuhnsw/aux.py of js1010/cuhnsw (get_logger :18-36, Option :79-119,
+get_opt_as_proto :60-67, proto_to_dict :69-72 there; Apache-2.0, Copyright (c) 2020 Jisang Yoon),
+written anew.  The reference validates the
 option dict by parsing it into a protobuf message generated from
 cuhnsw/proto/config.proto; the generated module needs protoc, so the schema is
 restated here as a typed table with the same field names, types and defaults,
@@ -12,23 +13,22 @@ import logging
 import re
 
 
+_LEVELS = {1: logging.WARNING, 2: logging.INFO, 3: logging.DEBUG}
+_LOG_FORMAT = "[%(levelname)-8s] %(asctime)s [%(filename)s] [%(funcName)s:%(lineno)d]%(message)s"
+
+
 def get_logger(name=__file__, level=2):
-  if level == 1:
-    level = logging.WARNING
-  elif level == 2:
-    level = logging.INFO
-  elif level == 3:
-    level = logging.DEBUG
+  """Logger that writes to stderr.  ``level`` follows the option ``py_log_level``: 1 = warnings,
+  2 = info, 3 = debug (the numbering of the reference's aux.get_logger); other values are passed to
+  ``logging`` as they are.  A logger that already has a handler is returned unchanged."""
   logger = logging.getLogger(name)
-  if logger.handlers:
-    return logger
-  logger.setLevel(level)
-  sh0 = logging.StreamHandler()
-  sh0.setLevel(level)
-  formatter = logging.Formatter("[%(levelname)-8s] %(asctime)s [%(filename)s] [%(funcName)s:%(lineno)d]"
-                                "%(message)s", "%Y-%m-%d %H:%M:%S")
-  sh0.setFormatter(formatter)
-  logger.addHandler(sh0)
+  if not logger.handlers:
+    threshold = _LEVELS.get(level, level)
+    handler = logging.StreamHandler()
+    handler.setLevel(threshold)
+    handler.setFormatter(logging.Formatter(_LOG_FORMAT, "%Y-%m-%d %H:%M:%S"))
+    logger.setLevel(threshold)
+    logger.addHandler(handler)
   return logger
 
 
@@ -72,6 +72,8 @@ EXTENSIONS = {
   "search_team": (int, -1),
   "search_schedule": (bool, True),
   "row_dtype": (str, "f32"),
+  # GPUs that hold a replica of the index and share every host-buffer search; empty = one GPU (device_id)
+  "devices": (list, ()),
 }
 ALIASES = {"heuristic_coff": "heuristic_coef"}
 
@@ -80,8 +82,8 @@ class ConfigProto:
   """Attribute bag with the fields of the reference's ConfigProto message."""
 
   def __init__(self):
-    for key, (_, default) in {**SCHEMA, **EXTENSIONS}.items():
-      object.__setattr__(self, key, default)
+    for key, (typ, default) in {**SCHEMA, **EXTENSIONS}.items():
+      object.__setattr__(self, key, list(default) if typ is list else default)
 
   def __setattr__(self, key, value):
     table = {**SCHEMA, **EXTENSIONS}
@@ -103,6 +105,10 @@ def _coerce(key, typ, value):
         isinstance(value, float) and float(value).is_integer()):
       raise TypeError(f"option {key}: expected int, got {value!r}")
     return int(value)
+  if typ is list:
+    if isinstance(value, (str, bytes)) or not all(isinstance(v, int) and not isinstance(v, bool) for v in value):
+      raise TypeError(f"option {key}: expected a list of ints, got {value!r}")
+    return [int(v) for v in value]
   if typ is float:
     if isinstance(value, bool) or not isinstance(value, (int, float)):
       raise TypeError(f"option {key}: expected number, got {value!r}")
@@ -131,36 +137,33 @@ def copy_proto(proto):
 
 
 class Option(dict):
-  """dict with attribute access; file names are loaded as JSON (aux.py:79-119)."""
+  """Options as a dict whose keys also read and write as attributes (``opt.max_m``); a missing key
+  reads as None.  Positional arguments are dicts or names of JSON files (comments and trailing commas
+  allowed); nested dicts become ``Option`` too.  Same behaviour as the reference's aux.Option."""
 
-  def __init__(self, *args, **kwargs):
-    args = [arg if isinstance(arg, dict) else load_json_file(arg) for arg in args]
-    super().__init__(*args, **kwargs)
-    for arg in args:
-      for k, val in arg.items():
-        self[k] = Option(val) if isinstance(val, dict) else val
-    for k, val in kwargs.items():
-      self[k] = Option(val) if isinstance(val, dict) else val
+  def __init__(self, *sources, **fields):
+    super().__init__()
+    for src in sources:
+      self.update(src if isinstance(src, dict) else load_json_file(src))
+    self.update(fields)
 
-  def __getattr__(self, attr):
-    return self.get(attr)
-
-  def __setattr__(self, key, value):
-    self.__setitem__(key, value)
+  def update(self, other=(), **fields):  # route every entry through __setitem__
+    for key, value in dict(other, **fields).items():
+      self[key] = value
 
   def __setitem__(self, key, value):
-    super().__setitem__(key, value)
-    self.__dict__.update({key: value})
+    super().__setitem__(key, Option(value) if isinstance(value, dict) and not isinstance(value, Option) else value)
 
-  def __delattr__(self, item):
-    self.__delitem__(item)
+  def __getattr__(self, name):
+    if name.startswith("__"):  # pickle and copy probe for dunder hooks
+      raise AttributeError(name)
+    return self.get(name)
 
-  def __delitem__(self, key):
-    super().__delitem__(key)
-    del self.__dict__[key]
+  def __setattr__(self, name, value):
+    self[name] = value
 
-  def __getstate__(self):
-    return vars(self)
-
-  def __setstate__(self, state):
-    vars(self).update(state)
+  def __delattr__(self, name):
+    try:
+      del self[name]
+    except KeyError:
+      raise AttributeError(name) from None

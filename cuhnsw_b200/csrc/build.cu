@@ -510,13 +510,13 @@ cudaError_t launch_build_batch(const BuildLevel& L, const BuildScratch& S, long 
 // ---------------------------------------------------------------------------
 // small utility kernels
 // ---------------------------------------------------------------------------
-__global__ void pad_rows_kernel(const float* src, float* dst, long long n, int d, int vstride) {
+__global__ void pad_rows_kernel(const float* src, long long src_stride, float* dst, long long n, int d, int vstride) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long total = n * vstride;
   for (; idx < total; idx += (long long)gridDim.x * blockDim.x) {
     long long r = idx / vstride;
     int c = (int)(idx % vstride);
-    dst[idx] = (c < d) ? src[r * d + c] : 0.0f;
+    dst[idx] = (c < d) ? src[r * src_stride + c] : 0.0f;
   }
 }
 __global__ void unpad_rows_kernel(const float* src, float* dst, long long n, int d, int vstride) {
@@ -530,13 +530,14 @@ __global__ void unpad_rows_kernel(const float* src, float* dst, long long n, int
 }
 // half rows: rounded to nearest even and stored in the paired-column layout of RowF16 (the rows were
 // cleared beforehand, so the padding reads zero)
-__global__ void pad_rows_f16_kernel(const float* src, __half* dst, long long n, int d, int vstride) {
+__global__ void pad_rows_f16_kernel(const float* src, long long src_stride, __half* dst, long long n, int d,
+                                    int vstride) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long total = n * d;
   for (; idx < total; idx += (long long)gridDim.x * blockDim.x) {
     long long r = idx / d;
     int e = (int)(idx % d);
-    dst[r * vstride + RowF16::position(d, e)] = __float2half_rn(src[idx]);
+    dst[r * vstride + RowF16::position(d, e)] = __float2half_rn(src[r * src_stride + e]);
   }
 }
 __global__ void unpad_rows_f16_kernel(const __half* src, float* dst, long long n, int d, int vstride) {
@@ -546,6 +547,28 @@ __global__ void unpad_rows_f16_kernel(const __half* src, float* dst, long long n
     long long r = idx / d;
     int e = (int)(idx % d);
     dst[idx] = __half2float(src[r * vstride + RowF16::position(d, e)]);
+  }
+}
+__global__ void unpack_links_kernel(const unsigned* __restrict__ records, long long rec_words, long long count,
+                                    long long first, int max_m0, long long n, int* __restrict__ rows, int stride,
+                                    int* __restrict__ labels, unsigned long long* bad) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = count * stride;
+  for (; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / stride;
+    const int j = (int)(idx % stride);
+    const unsigned* rec = records + r * rec_words;
+    const unsigned deg = rec[0] & 0xffffu;  // hnswlib keeps flags in the upper half of this word
+    int id = -1;
+    if (deg > (unsigned)max_m0) {
+      atomicMin(bad, (unsigned long long)(first + r + 1));
+    } else if ((unsigned)j < deg) {
+      const unsigned v = rec[1 + j];
+      if ((long long)v >= n) atomicMin(bad, (unsigned long long)(first + r + 1));
+      else id = (int)v;
+    }
+    rows[idx] = id;
+    if (j == 0 && labels) labels[r] = (int)rec[rec_words - 2];  // low word of the 64-bit label
   }
 }
 __global__ void fill_i32_kernel(int* p, long long n, int v) {
@@ -559,16 +582,26 @@ static unsigned blocks_for(long long total) {
   if (b < 1) b = 1;
   return (unsigned)b;
 }
-cudaError_t launch_pad_rows(const float* src, void* dst, long long n, int d, int vstride, int f16,
-                            cudaStream_t stream) {
+cudaError_t launch_pad_rows(const float* src, long long src_stride, void* dst, long long n, int d, int vstride,
+                            int f16, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
   if (f16) {
     cudaError_t e = cudaMemsetAsync(dst, 0, (size_t)n * vstride * sizeof(__half), stream);
     if (e != cudaSuccess) return e;
-    pad_rows_f16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(src, static_cast<__half*>(dst), n, d, vstride);
+    pad_rows_f16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(src, src_stride, static_cast<__half*>(dst), n, d,
+                                                               vstride);
   } else {
-    pad_rows_kernel<<<blocks_for(n * vstride), 256, 0, stream>>>(src, static_cast<float*>(dst), n, d, vstride);
+    pad_rows_kernel<<<blocks_for(n * vstride), 256, 0, stream>>>(src, src_stride, static_cast<float*>(dst), n, d,
+                                                                 vstride);
   }
+  return cudaGetLastError();
+}
+cudaError_t launch_unpack_links(const unsigned* records, long long rec_words, long long count, long long first,
+                                int max_m0, long long n, int* rows, int stride, int* labels,
+                                unsigned long long* bad, cudaStream_t stream) {
+  if (count <= 0) return cudaSuccess;
+  unpack_links_kernel<<<blocks_for(count * stride), 256, 0, stream>>>(records, rec_words, count, first, max_m0, n,
+                                                                      rows, stride, labels, bad);
   return cudaGetLastError();
 }
 cudaError_t launch_unpad_rows(const void* src, float* dst, long long n, int d, int vstride, int f16,

@@ -104,7 +104,7 @@ int Engine::EnsureDevice() {
   return kOk;
 }
 
-int Engine::Init(const char* opt_path) {
+int Engine::Init(const char* opt_path, int device_override) {
   if (!opt_path) return Fail(kInvalidArgument, "null option path");
   std::ifstream in(opt_path);
   if (!in.is_open()) return Fail(kIoError, std::string("cannot open option file ") + opt_path);
@@ -135,6 +135,17 @@ int Engine::Init(const char* opt_path) {
   o.batch_max = (long long)js.number("batch_max", (double)o.batch_max);
   o.ramp_div = (long long)js.number("ramp_div", (double)o.ramp_div);
   o.device_id = (int)js.number("device_id", o.device_id);
+  for (double v : js.numbers("devices")) {
+    if (v < 0 || v > 1023 || v != std::floor(v)) return Fail(kInvalidOption, "devices must list CUDA device numbers");
+    o.devices.push_back((int)v);
+  }
+  if (!o.devices.empty() && o.device_id >= 0 && o.device_id != o.devices[0])
+    return Fail(kInvalidOption, "device_id and devices[0] disagree");
+  if (!o.devices.empty()) o.device_id = o.devices[0];
+  if (device_override >= 0) {  // a replica of a multi-GPU handle: same options, its own GPU
+    o.device_id = device_override;
+    o.devices.clear();
+  }
   opt_.c_log_level = o.c_log_level;
   if (o.dist_type == "dot") dist_type_ = 0;
   else if (o.dist_type == "l2") dist_type_ = 1;
@@ -171,16 +182,8 @@ int Engine::SetData(const float* data, long long num_data, int num_dims) {
   if (!data && num_data > 0) return Fail(kInvalidArgument, "null data");
   if (num_data < 0 || num_dims < 1) return Fail(kInvalidArgument, "data must be a 2-d array with at least one column");
   if (num_data >= (1ll << 31) - 1) return Fail(kUnsupported, "at most 2^31 - 2 rows per index");
-  int rc = EnsureDevice();
+  int rc = AllocRows(num_data, num_dims);
   if (rc) return rc;
-  n_ = num_data;
-  d_ = num_dims;
-  f16_ = opt_.row_dtype == "f16";
-  vstride_ = row_stride_elements(num_dims, f16_ ? 1 : 0);  // rows start on 32-byte sectors
-  has_levels_ = has_graph_ = labelled_ = false;
-  labels_h_.clear();
-  labels_d_.release();
-  CU(vec_.alloc(((size_t)n_ * vstride_ * (f16_ ? 2 : 4) + 3) / 4));
   // stage through a bounded device buffer and pad rows on the device
   const long long rows_per_chunk = std::max<long long>(1, (64ll << 20) / num_dims);
   DevBuf<float> raw;
@@ -189,11 +192,26 @@ int Engine::SetData(const float* data, long long num_data, int num_dims) {
     long long r = std::min(rows_per_chunk, n_ - s);
     CU(cudaMemcpyAsync(raw.get(), data + (size_t)s * num_dims, (size_t)r * num_dims * sizeof(float),
                        cudaMemcpyHostToDevice, stream_));
-    CU(launch_pad_rows(raw.get(), RowPtr(s), r, num_dims, vstride_, f16_ ? 1 : 0, stream_));
+    CU(launch_pad_rows(raw.get(), num_dims, RowPtr(s), r, num_dims, vstride_, f16_ ? 1 : 0, stream_));
     CU(cudaStreamSynchronize(stream_));
   }
   has_data_ = true;
   Log(3, "copied data (%lld x %d), row stride %d %s", n_, d_, vstride_, f16_ ? "halves" : "floats");
+  return kOk;
+}
+
+// Device storage of num_data rows; whatever graph the handle held is dropped.
+int Engine::AllocRows(long long num_data, int num_dims) {
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  n_ = num_data;
+  d_ = num_dims;
+  f16_ = opt_.row_dtype == "f16";
+  vstride_ = row_stride_elements(num_dims, f16_ ? 1 : 0);  // rows start on 32-byte sectors
+  has_data_ = has_levels_ = has_graph_ = labelled_ = false;
+  labels_h_.clear();
+  labels_d_.release();
+  CU(vec_.alloc(((size_t)n_ * vstride_ * (f16_ ? 2 : 4) + 3) / 4));
   return kOk;
 }
 
@@ -415,7 +433,7 @@ int Engine::SearchGraphDevice(const float* d_q, long long nq, int topk, int ef, 
   if (n_ == 0) {
     CU(cudaMemsetAsync(d_found, 0, (size_t)nq * sizeof(int), stream_));
     CU(launch_fill_i32(d_nns, nq * topk, -1, stream_));
-    CU(cudaMemsetAsync(d_dist, 0x7f, (size_t)nq * topk * sizeof(float), stream_));
+    CU(launch_fill_i32(reinterpret_cast<int*>(d_dist), nq * topk, 0x7f800000, stream_));  // +inf
     return kOk;
   }
   int vsize = 0;
@@ -610,6 +628,16 @@ int Engine::SaveIndex(const char* path) {
   CU(cudaStreamSynchronize(stream_));
   std::FILE* f = std::fopen(path, "wb");
   if (!f) return Fail(kIoError, std::string("cannot open ") + path + " for writing");
+  // closes the file on every way out; a file that was not written to the end is removed
+  struct Guard {
+    std::FILE* f;
+    const char* path;
+    bool done = false;
+    ~Guard() {
+      if (f) std::fclose(f);
+      if (!done) std::remove(path);
+    }
+  } guard{f, path};
   const int m = opt_.max_m, m0 = opt_.max_m0;
   const size_t rec = 4 + 4 * (size_t)m0 + 4 * (size_t)d_ + 8;
   FileHeader h;
@@ -684,8 +712,10 @@ int Engine::SaveIndex(const char* path) {
     }
     ok = std::fwrite(lbuf.data(), 1, lbuf.size(), f) == lbuf.size();
   }
+  guard.f = nullptr;
   ok = (std::fclose(f) == 0) && ok;
   if (!ok) return Fail(kIoError, std::string("short write to ") + path);
+  guard.done = true;
   Log(3, "saved index to %s", path);
   return kOk;
 }
@@ -710,11 +740,14 @@ int Engine::LoadIndex(const char* path) {
   if (h.offset_data != 4 + 4 * h.max_m0 || h.label_offset < h.offset_data || (h.label_offset - h.offset_data) % 4 ||
       h.size_data_per_element != h.label_offset + 8)
     return Fail(kParseError, "index file: inconsistent record layout");
+  // sizes are checked by division, so that a crafted header cannot overflow the products
+  if (h.size_data_per_element > (uint64_t)fsize || h.cur_element_count >= (1ull << 31) - 1)
+    return Fail(kParseError, "index file: bad element count or dimension");
   const long long n = (long long)h.cur_element_count;
   const int d = (int)((h.label_offset - h.offset_data) / 4);
   const size_t rec = (size_t)h.size_data_per_element;
-  if (d < 1 || n < 0 || n >= (1ll << 31) - 1) return Fail(kParseError, "index file: bad element count or dimension");
-  if ((long long)sizeof(h) + n * (long long)rec > fsize) return Fail(kIoError, "index file: truncated level-0 block");
+  if (d < 1) return Fail(kParseError, "index file: bad element count or dimension");
+  if (n > (fsize - (long long)sizeof(h)) / (long long)rec) return Fail(kIoError, "index file: truncated level-0 block");
   if (n > 0 && (h.enterpoint_node >= (uint64_t)n || h.maxlevel < 0 || h.maxlevel > 64))
     return Fail(kParseError, "index file: bad enter point or level");
   const int m = (int)h.max_m, m0 = (int)h.max_m0;
@@ -724,92 +757,164 @@ int Engine::LoadIndex(const char* path) {
   opt_.ef_construction = (int)std::min<uint64_t>(h.ef_construction, kMaxEf);
   opt_.level_mult = h.mult;
 
-  const int stride0 = round_up(m0, 8);
-  std::vector<float> vecs((size_t)n * d);
-  std::vector<int> rows0((size_t)n * stride0, -1);
+  // Level-0 block: a chunk of records goes to the device as it lies in the file and is taken apart
+  // there (vectors into padded rows, neighbour slots into -1 padded adjacency rows, labels); the host
+  // keeps only the 64-bit labels, which a later save_index writes back unchanged.
+  int rc = AllocRows(n, d);
+  if (rc) return rc;
+  stride0_ = round_up(m0, 8);
+  strideU_ = round_up(m, 8);
+  CU(rows0_.alloc((size_t)std::max<long long>(n, 1) * stride0_));
+  CU(labels_d_.alloc((size_t)std::max<long long>(n, 1)));
   std::vector<long long> labels((size_t)n);
+  const long long rec_words = (long long)(rec / 4);
   {
     const long long chunk = std::max<long long>(1, (32ll << 20) / (long long)rec);
-    std::vector<unsigned char> buf((size_t)std::min(chunk, std::max<long long>(n, 1)) * rec);
+    const size_t rows_in_chunk = (size_t)std::min(chunk, std::max<long long>(n, 1));
+    std::vector<unsigned char> buf(rows_in_chunk * rec);
+    DevBuf<unsigned> raw;
+    DevBuf<unsigned long long> bad;
+    CU(raw.alloc(rows_in_chunk * (size_t)rec_words));
+    CU(bad.alloc(1));
+    CU(cudaMemsetAsync(bad.get(), 0xff, sizeof(unsigned long long), stream_));
     for (long long s = 0; s < n; s += chunk) {
       const long long r = std::min(chunk, n - s);
       if (std::fread(buf.data(), rec, (size_t)r, f) != (size_t)r) return Fail(kIoError, "index file: short read");
+      CU(cudaMemcpyAsync(raw.get(), buf.data(), (size_t)r * rec, cudaMemcpyHostToDevice, stream_));
+      CU(launch_unpack_links(raw.get(), rec_words, r, s, m0, n, rows0_.get() + (size_t)s * stride0_, stride0_,
+                             labels_d_.get() + s, bad.get(), stream_));
+      CU(launch_pad_rows(reinterpret_cast<const float*>(raw.get() + 1 + m0), rec_words, RowPtr(s), r, d, vstride_,
+                         f16_ ? 1 : 0, stream_));
       for (long long i = 0; i < r; ++i) {
-        const unsigned char* o = buf.data() + (size_t)i * rec;
-        uint32_t deg;
-        std::memcpy(&deg, o, 4);
-        deg &= 0xffffu;  // hnswlib keeps flags in the upper half of this word
-        if (deg > (uint32_t)m0) return Fail(kParseError, "index file: degree above maxM0");
-        int* row = rows0.data() + (size_t)(s + i) * stride0;
-        for (uint32_t j = 0; j < deg; ++j) {
-          uint32_t id;
-          std::memcpy(&id, o + 4 + 4 * (size_t)j, 4);
-          if (id >= (uint64_t)n) return Fail(kParseError, "index file: neighbour id out of range");
-          row[j] = (int)id;
-        }
-        std::memcpy(vecs.data() + (size_t)(s + i) * d, o + 4 + 4 * (size_t)m0, 4 * (size_t)d);
         uint64_t label;
-        std::memcpy(&label, o + rec - 8, 8);
+        std::memcpy(&label, buf.data() + (size_t)(i + 1) * rec - 8, 8);
         labels[(size_t)(s + i)] = (long long)label;
       }
+      CU(cudaStreamSynchronize(stream_));  // buf and raw are reused by the next chunk
+    }
+    unsigned long long first_bad = 0;
+    CU(cudaMemcpy(&first_bad, bad.get(), sizeof(first_bad), cudaMemcpyDeviceToHost));
+    if (first_bad != ~0ull) {
+      std::ostringstream os;
+      os << "index file: record " << (first_bad - 1) << " has a degree above maxM0 or a neighbour id out of range";
+      return Fail(kParseError, os.str());
     }
   }
-  // upper layers
+  has_data_ = true;
+  // Upper layers: per node a byte count and that many bytes of (degree, maxM slots) lists.  Only the
+  // nodes above level 0 carry any (one in maxM0 or so), so their rows are collected on the host in
+  // the flat layout and uploaded once.
   const size_t per_link = 4 + 4 * (size_t)m;
-  std::vector<int> levels((size_t)n, 0);
-  std::vector<std::vector<unsigned char>> lists((size_t)n);
+  levels_h_.assign((size_t)n, 0);
+  std::vector<int> rowsU;
+  std::vector<unsigned char> lbuf;
   for (long long i = 0; i < n; ++i) {
     uint32_t nbytes;
     if (std::fread(&nbytes, 4, 1, f) != 1) return Fail(kIoError, "index file: truncated link lists");
     if (nbytes % per_link || nbytes / per_link > 64) return Fail(kParseError, "index file: bad link list size");
-    levels[(size_t)i] = (int)(nbytes / per_link);
-    if (nbytes) {
-      lists[(size_t)i].resize(nbytes);
-      if (std::fread(lists[(size_t)i].data(), 1, nbytes, f) != nbytes)
-        return Fail(kIoError, "index file: truncated link lists");
-    }
-  }
-  int rc = SetData(vecs.data(), n, d);
-  if (rc) return rc;
-  levels_h_ = levels;
-  max_level_ = h.maxlevel;
-  enter_point_ = n > 0 ? (int)h.enterpoint_node : 0;
-  if (n > 0 && levels[(size_t)enter_point_] < max_level_)
-    return Fail(kParseError, "index file: enter point does not reach the top level");
-  rc = AllocGraph();
-  if (rc) return rc;
-  std::vector<int> rowsU((size_t)std::max<long long>(total_upper_, 1) * strideU_, -1);
-  for (long long i = 0; i < n; ++i) {
-    for (int l = 0; l < levels[(size_t)i]; ++l) {
-      const unsigned char* o = lists[(size_t)i].data() + per_link * (size_t)l;
+    const int lv = (int)(nbytes / per_link);
+    if (lv > h.maxlevel) return Fail(kParseError, "index file: a node lies above the file's top level");
+    levels_h_[(size_t)i] = lv;
+    if (!nbytes) continue;
+    lbuf.resize(nbytes);
+    if (std::fread(lbuf.data(), 1, nbytes, f) != nbytes) return Fail(kIoError, "index file: truncated link lists");
+    for (int l = 0; l < lv; ++l) {
+      const unsigned char* o = lbuf.data() + per_link * (size_t)l;
       uint32_t deg;
       std::memcpy(&deg, o, 4);
       deg &= 0xffffu;
       if (deg > (uint32_t)m) return Fail(kParseError, "index file: degree above maxM");
-      int* row = rowsU.data() + ((size_t)upper_base_h_[(size_t)i] + l) * strideU_;
+      const size_t at = rowsU.size();
+      rowsU.resize(at + (size_t)strideU_, -1);
       for (uint32_t j = 0; j < deg; ++j) {
         uint32_t id;
         std::memcpy(&id, o + 4 + 4 * (size_t)j, 4);
-        if (id >= (uint64_t)n || levels[id] < l + 1) return Fail(kParseError, "index file: bad upper-layer neighbour");
-        row[j] = (int)id;
+        if (id >= (uint64_t)n) return Fail(kParseError, "index file: bad upper-layer neighbour");
+        rowsU[at + j] = (int)id;
       }
     }
   }
-  if (n > 0) {
-    CU(cudaMemcpy(rows0_.get(), rows0.data(), rows0.size() * sizeof(int), cudaMemcpyHostToDevice));
-    if (total_upper_ > 0)
-      CU(cudaMemcpy(rowsU_.get(), rowsU.data(), (size_t)total_upper_ * strideU_ * sizeof(int), cudaMemcpyHostToDevice));
-    std::vector<int> lab32((size_t)n);
-    for (long long i = 0; i < n; ++i) lab32[(size_t)i] = (int)labels[(size_t)i];  // cuhnsw_base.cu:322-324
-    CU(labels_d_.alloc((size_t)n));
-    CU(cudaMemcpy(labels_d_.get(), lab32.data(), (size_t)n * sizeof(int), cudaMemcpyHostToDevice));
+  max_level_ = h.maxlevel;
+  enter_point_ = n > 0 ? (int)h.enterpoint_node : 0;
+  if (n > 0 && levels_h_[(size_t)enter_point_] < max_level_)
+    return Fail(kParseError, "index file: enter point does not reach the top level");
+  // a neighbour on layer l must itself reach layer l (its row there is read during the descent)
+  {
+    size_t at = 0;
+    for (long long i = 0; i < n; ++i)
+      for (int l = 1; l <= levels_h_[(size_t)i]; ++l, at += (size_t)strideU_)
+        for (int j = 0; j < m && rowsU[at + j] >= 0; ++j)
+          if (levels_h_[(size_t)rowsU[at + j]] < l) return Fail(kParseError, "index file: bad upper-layer neighbour");
   }
-  labels_h_ = labels;
+  upper_base_h_.assign((size_t)n, 0);
+  long long acc = 0;
+  for (long long i = 0; i < n; ++i) {
+    upper_base_h_[(size_t)i] = (int)acc;
+    acc += levels_h_[(size_t)i];
+    if (acc > (1ll << 30)) return Fail(kUnsupported, "too many upper-layer rows");
+  }
+  total_upper_ = acc;
+  CU(rowsU_.alloc((size_t)std::max<long long>(total_upper_, 1) * strideU_));
+  CU(levels_d_.alloc((size_t)std::max<long long>(n, 1)));
+  CU(upper_base_d_.alloc((size_t)std::max<long long>(n, 1)));
+  if (total_upper_ > 0)
+    CU(cudaMemcpy(rowsU_.get(), rowsU.data(), (size_t)total_upper_ * strideU_ * sizeof(int), cudaMemcpyHostToDevice));
+  else
+    CU(launch_fill_i32(rowsU_.get(), strideU_, -1, stream_));
+  if (n > 0) {
+    CU(cudaMemcpy(levels_d_.get(), levels_h_.data(), (size_t)n * sizeof(int), cudaMemcpyHostToDevice));
+    CU(cudaMemcpy(upper_base_d_.get(), upper_base_h_.data(), (size_t)n * sizeof(int), cudaMemcpyHostToDevice));
+  }
+  CU(cudaStreamSynchronize(stream_));
+  labels_h_.swap(labels);
   labelled_ = true;
   has_levels_ = true;
   has_graph_ = true;
   Log(3, "loaded %s: num_data %lld, num_dims %d, max_m %d, max_m0 %d, enter_point %d, max_level %d", path, n_, d_, m,
       m0, enter_point_, max_level_);
+  return kOk;
+}
+
+// Replica of another engine's index on this engine's GPU: same rows, graph and labels, copied device to
+// device.  The two engines must have been initialised from the same options.
+int Engine::CloneFrom(const Engine& src) {
+  if (!inited_) return Fail(kBadState, "init() must be called first");
+  if (!src.has_graph_) return Fail(kBadState, "nothing to replicate: the source has no graph");
+  opt_.max_m = src.opt_.max_m;
+  opt_.max_m0 = src.opt_.max_m0;
+  opt_.ef_construction = src.opt_.ef_construction;
+  opt_.level_mult = src.opt_.level_mult;
+  int rc = AllocRows(src.n_, src.d_);
+  if (rc) return rc;
+  if (f16_ != src.f16_) return Fail(kBadState, "replica and source store rows in different types");
+  stride0_ = src.stride0_;
+  strideU_ = src.strideU_;
+  max_level_ = src.max_level_;
+  enter_point_ = src.enter_point_;
+  total_upper_ = src.total_upper_;
+  levels_h_ = src.levels_h_;
+  upper_base_h_ = src.upper_base_h_;
+  labels_h_ = src.labels_h_;
+  auto copy = [&](void* dst, const void* from, size_t bytes) {
+    return bytes ? cudaMemcpyPeer(dst, device_, from, src.device_, bytes) : cudaSuccess;
+  };
+  const size_t one = (size_t)std::max<long long>(n_, 1);
+  CU(rows0_.alloc(one * stride0_));
+  CU(rowsU_.alloc((size_t)std::max<long long>(total_upper_, 1) * strideU_));
+  CU(levels_d_.alloc(one));
+  CU(upper_base_d_.alloc(one));
+  CU(copy(vec_.get(), src.vec_.get(), vec_.size() * sizeof(float)));
+  CU(copy(rows0_.get(), src.rows0_.get(), rows0_.size() * sizeof(int)));
+  CU(copy(rowsU_.get(), src.rowsU_.get(), rowsU_.size() * sizeof(int)));
+  CU(copy(levels_d_.get(), src.levels_d_.get(), levels_d_.size() * sizeof(int)));
+  CU(copy(upper_base_d_.get(), src.upper_base_d_.get(), upper_base_d_.size() * sizeof(int)));
+  if (src.labelled_) {
+    CU(labels_d_.alloc(one));
+    CU(copy(labels_d_.get(), src.labels_d_.get(), labels_d_.size() * sizeof(int)));
+  }
+  CU(cudaDeviceSynchronize());
+  labelled_ = src.labelled_;
+  has_data_ = has_levels_ = has_graph_ = true;
   return kOk;
 }
 

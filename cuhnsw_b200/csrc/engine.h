@@ -53,6 +53,8 @@ struct Options {
   // schedule to the next (0.955-0.961 at ef 300; 100 000 x 50: 0.990 / 0.993 / 0.987 / 0.995 with 16 / 4 / 2 / 1).
   long long ramp_div = 4;
   int device_id = -1;       // -1 = current device
+  // GPUs that each hold a replica of the index; a host-buffer search is split over them.  Empty: one GPU.
+  std::vector<int> devices;
 };
 
 template <class T>
@@ -89,7 +91,13 @@ class Engine {
   Engine();
   ~Engine();
 
-  int Init(const char* opt_path);
+  // device_override >= 0: use that GPU whatever the option file says (replicas of a multi-GPU handle)
+  int Init(const char* opt_path, int device_override = -1);
+  // makes this engine a copy of src's index on its own GPU (device-to-device)
+  int CloneFrom(const Engine& src);
+  bool has_graph() const { return has_graph_; }
+  long long num_data() const { return n_; }
+  int num_dims() const { return d_; }
   int SetData(const float* data, long long num_data, int num_dims);
   int SetRandomLevels(const int* levels);
   int BuildGraph();
@@ -120,6 +128,7 @@ class Engine {
   int Fail(int code, const std::string& msg);
   int FailCuda(cudaError_t e, const char* what);
   int EnsureDevice();
+  int AllocRows(long long num_data, int num_dims);
   int AllocGraph();
   int ResolveVsize(int requested_cap, long long nq, int* vsize) const;  // nq < 0: construction
   GraphView View() const;

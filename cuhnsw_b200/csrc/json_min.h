@@ -1,20 +1,22 @@
 // Minimal reader for the flat JSON object the Python layer writes as its option
 // file (cuhnsw/pyhnsw.py:36-39 dumps the option message; cpp/src/cuhnsw_base.cu:67-106
 // reads it back).  Supports one object of string keys mapped to numbers, booleans,
-// strings or null; anything else is a parse error.
+// strings, null or arrays of numbers; anything else is a parse error.
 #pragma once
 #include <cctype>
 #include <cstdlib>
 #include <map>
 #include <string>
+#include <vector>
 
 namespace hnsw {
 
 struct JsonValue {
-  enum Kind { kNull, kBool, kNumber, kString } kind = kNull;
+  enum Kind { kNull, kBool, kNumber, kString, kNumbers } kind = kNull;
   double num = 0.0;
   bool b = false;
   std::string str;
+  std::vector<double> nums;
 };
 
 class FlatJson {
@@ -57,6 +59,14 @@ class FlatJson {
     if (it->second.kind == JsonValue::kBool) return it->second.b;
     if (it->second.kind == JsonValue::kNumber) return it->second.num != 0.0;
     return dflt;
+  }
+  // array of numbers; a single number reads as an array of one
+  std::vector<double> numbers(const std::string& k) const {
+    auto it = values_.find(k);
+    if (it == values_.end()) return {};
+    if (it->second.kind == JsonValue::kNumbers) return it->second.nums;
+    if (it->second.kind == JsonValue::kNumber) return {it->second.num};
+    return {};
   }
   std::string string(const std::string& k, const std::string& dflt) const {
     auto it = values_.find(k);
@@ -131,6 +141,21 @@ class FlatJson {
     if (c == '"') {
       v->kind = JsonValue::kString;
       return str(&v->str);
+    }
+    if (c == '[') {
+      ++i_;
+      v->kind = JsonValue::kNumbers;
+      ws();
+      if (eat(']')) return true;
+      for (;;) {
+        ws();
+        JsonValue item;
+        if (end() || cur() == '[' || !value(&item) || item.kind != JsonValue::kNumber) return false;
+        v->nums.push_back(item.num);
+        ws();
+        if (eat(',')) continue;
+        return eat(']');
+      }
     }
     if (literal("true")) {
       v->kind = JsonValue::kBool;

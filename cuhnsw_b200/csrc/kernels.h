@@ -126,17 +126,34 @@ cudaError_t launch_build_batch(const BuildLevel& L, const BuildScratch& S, long 
                                int sm_count, cudaStream_t stream);
 // elements per stored row: d rounded up to 8 floats, or whole pairs of chunk columns of halves
 int row_stride_elements(int d, int f16);
-// pads an unpadded n x d fp32 matrix into n x vstride rows of floats or halves, and back
-cudaError_t launch_pad_rows(const float* src, void* dst, long long n, int d, int vstride, int f16,
-                            cudaStream_t stream);
+// pads n fp32 rows of d elements (row r starts at src + r * src_stride; src_stride = d for a dense matrix,
+// the record length in words for rows embedded in index-file records) into n x vstride rows of floats or
+// halves, and back
+cudaError_t launch_pad_rows(const float* src, long long src_stride, void* dst, long long n, int d, int vstride,
+                            int f16, cudaStream_t stream);
 cudaError_t launch_unpad_rows(const void* src, float* dst, long long n, int d, int vstride, int f16,
                               cudaStream_t stream);
 cudaError_t launch_fill_i32(int* p, long long n, int v, cudaStream_t stream);
-// merges parts x nq x k per-shard rows (global ids, -1 = empty) into nq x k rows ordered by (distance, id)
-cudaError_t launch_merge_topk(const int* ids, const float* dist, int parts, long long nq, int k, int* out_ids,
-                              float* out_dist, int* out_found, cudaStream_t stream);
+// Level-0 records of an hnswlib index file, already on the device (`count` records of `rec_words` 32-bit words:
+// degree word, max_m0 neighbour slots, the vector, a 64-bit label): writes the -1 padded adjacency rows and
+// the labels truncated to int (cpp/src/cuhnsw_base.cu:300-324).  A degree above max_m0 or a neighbour id
+// outside [0, n) stores 1 + the record number of the first offender found in *bad (0 = file is sound).
+cudaError_t launch_unpack_links(const unsigned* records, long long rec_words, long long count, long long first,
+                                int max_m0, long long n, int* rows, int stride, int* labels,
+                                unsigned long long* bad, cudaStream_t stream);
+// merges per-shard rows (part p at ids/dist + p * part_stride, nq x k each, -1 = empty; offsets[p], when given,
+// turns shard-local ids into global ones) into nq x k rows ordered by (distance, id)
+cudaError_t launch_merge_topk(const int* ids, const float* dist, long long part_stride, const int* offsets, int parts,
+                              long long nq, int k, int* out_ids, float* out_dist, int* out_found,
+                              cudaStream_t stream);
 // out[i] = canonical distance between stored rows src[i] and dst[i]
 cudaError_t launch_batch_distance(const GraphView& g, const int* src, const int* dst, long long npairs, float* out,
                                   cudaStream_t stream);
+
+// self-tests of the candidate list and the visited table (host arrays in and out; see selftest.cu)
+cudaError_t selftest_list_host(int cap, const float* dist, const int* ids, const int* batch_begin, int nbatches,
+                               const int* expand, unsigned long long* out_keys, int* out_size, int* out_minpos,
+                               int* out_cursor);
+cudaError_t selftest_visited_host(int entries, long long n, const int* ids, int count, int* seen);
 
 }  // namespace hnsw

@@ -6,9 +6,12 @@
 
 namespace hnsw {
 
-// lists: parts x nq x k, already offset to global ids, -1 = empty slot.  One warp per query:
-// every candidate counts the keys smaller than its own and writes itself at that rank.
+// lists: per part nq x k ids (-1 = empty slot) and distances; part p starts at ids/dist + p * part_stride
+// (part_stride = nq * k for two dense parts x nq x k blocks, 2 * nq * k for the parts x 2 x nq x k buffer one
+// all-gather fills).  With `offsets`, ids are local to their shard and offsets[p] makes them global.  One
+// warp per query: every candidate counts the keys smaller than its own and writes itself at that rank.
 __global__ void __launch_bounds__(128) merge_topk_kernel(const int* __restrict__ ids, const float* __restrict__ dist,
+                                                         long long part_stride, const int* __restrict__ offsets,
                                                          int parts, long long nq, int k, int* __restrict__ out_ids,
                                                          float* __restrict__ out_dist, int* __restrict__ out_found) {
   extern __shared__ unsigned long long skeys[];
@@ -18,8 +21,9 @@ __global__ void __launch_bounds__(128) merge_topk_kernel(const int* __restrict__
   for (long long q = (long long)blockIdx.x * 4 + warp; q < nq; q += (long long)gridDim.x * 4) {
     for (int e = lane; e < total; e += 32) {
       int p = e / k, j = e % k;
-      size_t at = ((size_t)p * nq + q) * k + j;
+      size_t at = (size_t)p * part_stride + (size_t)q * k + j;
       int id = ids[at];
+      if (id >= 0 && offsets) id += offsets[p];
       mine[e] = id >= 0 ? mkkey(dist[at], id) : ~0ull;
     }
     __syncwarp();
@@ -50,8 +54,9 @@ __global__ void __launch_bounds__(128) merge_topk_kernel(const int* __restrict__
   }
 }
 
-cudaError_t launch_merge_topk(const int* ids, const float* dist, int parts, long long nq, int k, int* out_ids,
-                              float* out_dist, int* out_found, cudaStream_t stream) {
+cudaError_t launch_merge_topk(const int* ids, const float* dist, long long part_stride, const int* offsets, int parts,
+                              long long nq, int k, int* out_ids, float* out_dist, int* out_found,
+                              cudaStream_t stream) {
   if (nq <= 0) return cudaSuccess;
   size_t smem = (size_t)4 * parts * k * sizeof(unsigned long long);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
@@ -59,7 +64,8 @@ cudaError_t launch_merge_topk(const int* ids, const float* dist, int parts, long
   if (e != cudaSuccess) return e;
   long long blocks = (nq + 3) / 4;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  merge_topk_kernel<<<(unsigned)blocks, 128, smem, stream>>>(ids, dist, parts, nq, k, out_ids, out_dist, out_found);
+  merge_topk_kernel<<<(unsigned)blocks, 128, smem, stream>>>(ids, dist, part_stride, offsets, parts, nq, k, out_ids,
+                                                             out_dist, out_found);
   return cudaGetLastError();
 }
 

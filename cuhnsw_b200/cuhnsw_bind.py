@@ -12,8 +12,7 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# CUHNSW_B200_LIB selects another build of the same library (kernel tuning experiments)
-LIB_PATH = os.environ.get("CUHNSW_B200_LIB") or os.path.join(_HERE, "libcuhnsw_b200.so")
+LIB_PATH = os.path.join(_HERE, "libcuhnsw_b200.so")
 
 _f32p = ctypes.POINTER(ctypes.c_float)
 _i32p = ctypes.POINTER(ctypes.c_int32)
@@ -47,6 +46,14 @@ SIGNATURES = {
   "cuhnsw_merge_topk_device": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64,
                                                ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                ctypes.c_void_p]),
+  "cuhnsw_merge_topk_gathered_device": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
+                                                       ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p,
+                                                       ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_selftest_list_merge": (ctypes.c_int, [ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_selftest_visited": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int32,
+                                             ctypes.c_void_p]),
 }
 
 _lib = None
@@ -124,16 +131,27 @@ class CuHNSWBind:
       fpath = fpath.encode("utf8")
     self._check(self._lib.cuhnsw_load_index(self._h, fpath))
 
-  def search_knn(self, qdata, topk, ef_search, nns, distances, found):
+  def _search_args(self, qdata, topk, nns, distances, found):
+    """Validates what both host-buffer searches receive: the engine writes num_queries x topk items
+    through the raw output pointers and reads num_queries x num_dims floats of the queries."""
     q = np.ascontiguousarray(qdata, dtype=np.float32)
     if q.ndim not in (1, 2):
       raise RuntimeError("data array must be 1d / 2d shape")
     nq = 1 if q.ndim == 1 else q.shape[0]
+    if int(topk) < 1:
+      raise RuntimeError("topk must be at least 1")
+    num_dims = self.describe()["num_dims"]
+    if num_dims > 0 and q.shape[-1] != num_dims:
+      raise RuntimeError(f"queries have {q.shape[-1]} dimensions, the index has {num_dims}")
     for name, arr, dt in (("nns", nns, np.int32), ("distances", distances, np.float32), ("found", found, np.int32)):
       if not (isinstance(arr, np.ndarray) and arr.dtype == dt and arr.flags.c_contiguous and arr.flags.writeable):
         raise RuntimeError(f"{name} must be a writable C-contiguous {np.dtype(dt).name} array")
     if nns.size < nq * topk or distances.size < nq * topk or found.size < nq:
       raise RuntimeError("output arrays are too small")
+    return q, nq
+
+  def search_knn(self, qdata, topk, ef_search, nns, distances, found):
+    q, nq = self._search_args(qdata, topk, nns, distances, found)
     self._check(self._lib.cuhnsw_search_knn(self._h, q.ctypes.data, nq, topk, ef_search, nns.ctypes.data,
                                             distances.ctypes.data, found.ctypes.data))
 
@@ -146,10 +164,7 @@ class CuHNSWBind:
   def search_knn_noalloc(self, qdata, topk, ef_search, nns, distances, found):
     """search_knn for callers that cannot allocate device memory: device staging comes from a fixed
     4 MiB array inside the library (see cuhnsw_search_knn_noalloc in include/cuhnsw_b200.h)."""
-    q = np.ascontiguousarray(qdata, dtype=np.float32)
-    if q.ndim not in (1, 2):
-      raise RuntimeError("data array must be 1d / 2d shape")
-    nq = 1 if q.ndim == 1 else q.shape[0]
+    q, nq = self._search_args(qdata, topk, nns, distances, found)
     self._check(self._lib.cuhnsw_search_knn_noalloc(self._h, q.ctypes.data, nq, topk, ef_search, nns.ctypes.data,
                                                     distances.ctypes.data, found.ctypes.data))
 

@@ -6,7 +6,8 @@
  * of the last error of a handle is available from cuhnsw_last_error().  The
  * functions are exactly what a binding of the reference's host class needs:
  * each one names the reference method it stands for (paths inside the
- * reference project).  One handle owns one device-resident index on one GPU;
+ * reference project).  One handle owns one device-resident index on one GPU
+ * (plus replicas on further GPUs when the option `devices` lists them);
  * calls on one handle must not overlap.
  */
 #ifndef CUHNSW_B200_H_
@@ -28,7 +29,9 @@ enum {
   CUHNSW_INVALID_OPTION = -4,/* e.g. dist_type other than "dot" or "l2" */
   CUHNSW_CUDA_ERROR = -5,    /* includes "no CUDA device": there is no CPU path */
   CUHNSW_BAD_STATE = -6,     /* call order: init -> set_data -> set_random_levels -> build_graph */
-  CUHNSW_UNSUPPORTED = -7
+  CUHNSW_UNSUPPORTED = -7,
+  CUHNSW_OUT_OF_MEMORY = -8, /* host allocation failed inside the call */
+  CUHNSW_INTERNAL_ERROR = -9 /* an unexpected C++ exception was caught at the boundary */
 };
 
 /* CuHNSWBind() constructor + cuhnsw::CuHNSW::CuHNSW()  (cuhnsw/bindings.cc:20, cpp/src/cuhnsw_base.cu:13-62) */
@@ -40,7 +43,12 @@ const char* cuhnsw_last_error(const cuhnsw_handle* h);
 
 /* CuHNSWBind::Init -> CuHNSW::Init(opt_path)  (cuhnsw/bindings.cc:22-24, cpp/src/cuhnsw_base.cu:67-106).
  * opt_path: JSON object with the field names of cuhnsw/proto/config.proto:9-27.
- * IO/PARSE errors correspond to the reference returning false; INVALID_OPTION to its runtime_error. */
+ * IO/PARSE errors correspond to the reference returning false; INVALID_OPTION to its runtime_error.
+ * Keys beyond the reference's schema (all optional): device_id (GPU of the handle; default: the current device),
+ * devices (array of GPU numbers: the index is built or loaded on the first and copied to the others, and
+ * cuhnsw_search_knn cuts every batch into contiguous slices, one per listed GPU, searched at the same time by one
+ * host thread each; results equal the single-GPU results row for row; a GPU may be listed more than once),
+ * batch_max, ramp_div (insertion batch schedule), search_team, search_schedule, row_dtype ("f32", "f16", "bf16"). */
 int cuhnsw_init(cuhnsw_handle* h, const char* opt_path);
 
 /* CuHNSWBind::SetData -> CuHNSW::SetData  (cuhnsw/bindings.cc:26-33, cpp/src/cuhnsw_base.cu:108-128).
@@ -74,9 +82,11 @@ int cuhnsw_search_knn_device(cuhnsw_handle* h, const float* d_qdata, int64_t num
 
 /* Search for callers that must not allocate.  No counterpart in the reference (its SearchGraph allocates a dozen
  * device vectors per call, cpp/src/cuhnsw_build.cu:241-249).  Same arguments and results as cuhnsw_search_knn (host
- * buffers), but the call reaches no cudaMalloc/cudaFree or other allocating routine: the device copies of the
- * queries and results and the kernel's work ticket live in one fixed 4 MiB array inside the library image, which
- * every GPU that loads the library keeps until the process exits.  Meant for processes whose device memory is
+ * buffers), but once the index is in place (cuhnsw_set_data or cuhnsw_load_index has run on this handle: they
+ * create the handle's few words of device counters) the call itself reaches no cudaMalloc/cudaFree or other
+ * allocating routine: the device copies of the queries and results and the kernel's work ticket live in one
+ * fixed 4 MiB array inside the library image, which every GPU that loads the library keeps until the process
+ * exits.  Meant for processes whose device memory is
  * already owned by their own pool or capped by a budget (a late allocation would fail), and for loops that cannot
  * take the device-wide synchronisation an allocation implies.
  *  - Limit: 256 + 4*num_queries*num_dims + 8*num_queries*topk + 4*num_queries bytes (each term rounded up to
@@ -84,6 +94,10 @@ int cuhnsw_search_knn_device(cuhnsw_handle* h, const float* d_qdata, int64_t num
  *    CUHNSW_INVALID_ARGUMENT and a message that states both numbers.
  *  - The first call on a device looks up the array's device address (a one-time set-up per device); make that
  *    first call before any stream capture is started.
+ *  - The CUDA runtime loads a kernel into device memory the first time it is launched.  Which search kernel runs
+ *    depends on the row width class (<= 32, 64, 96, 128 floats, wider), row_dtype, reverse_cand and, for rows wider
+ *    than 128 floats, the batch size class; the first call of each combination therefore takes that memory and
+ *    belongs in the warm-up of a process that later runs with its pool full.
  *  - The array is shared by all handles and calls of the process on that device and keeps the previous call's
  *    contents; the call clears the one word that has to start at zero.  Calls that overlap on the GPU (two
  *    threads, two streams) race on it: issue them one after the other. */
@@ -121,6 +135,35 @@ double cuhnsw_last_build_seconds(const cuhnsw_handle* h);
 int cuhnsw_merge_topk_device(const int32_t* d_ids, const float* d_distances, int32_t parts, int64_t num_queries,
                              int32_t topk, int32_t* d_out_ids, float* d_out_distances, int32_t* d_out_found,
                              void* cuda_stream);
+
+/* The same merge, reading the buffer ONE all-gather fills: d_gathered is parts x 2 x num_queries x topk int32, block
+ * [p][0] the ids of shard p (local to the shard), block [p][1] the bit patterns of its distances; d_id_offsets[p]
+ * (may be NULL) is added to every valid id of shard p.  Each rank's search writes its two blocks in place, the
+ * collective (NCCL all-gather over NVLink) exchanges them, and this kernel reads them where they landed: no
+ * repacking copy on either side.  No counterpart in the reference (single-device). */
+int cuhnsw_merge_topk_gathered_device(const int32_t* d_gathered, const int32_t* d_id_offsets, int32_t parts,
+                                      int64_t num_queries, int32_t topk, int32_t* d_out_ids, float* d_out_distances,
+                                      int32_t* d_out_found, void* cuda_stream);
+
+/* Self-tests of the two shared-memory structures every walk uses, for checking them against a host model
+ * (host arrays in and out, runs on the current GPU, one warp).  They pin the semantics the reference spreads
+ * over PushNodeToSearchPq / CheckAlreadyExists / GetCand (cpp/include/cuda_utils_kernels.cuh:50-151,212-227:
+ * insert while there is room, else replace the largest key if the new one is smaller; no key twice; the next
+ * key to expand is the smallest unexpanded one) and CheckVisited (:185-210: may forget, never invents).
+ *
+ * list_merge: batch b holds the pairs [batch_begin[b], batch_begin[b+1]) (at most 32) of distances/ids and is
+ * merged in one step into a list of `capacity` keys; before it, the expand_before[b] smallest unexpanded keys
+ * are marked expanded.  out_keys (capacity slots): the final list, ascending by (distance, id); a key is
+ * ord(distance) << 32 | expanded << 31 | id with ord the order-preserving image of the float bits.
+ * out_first_position[b]: smallest position a key of batch b took, or capacity.  out_cursor: position of the
+ * smallest unexpanded key (= *out_size when there is none). */
+int cuhnsw_selftest_list_merge(int32_t capacity, const float* distances, const int32_t* ids,
+                               const int32_t* batch_begin, int32_t num_batches, const int32_t* expand_before,
+                               uint64_t* out_keys, int32_t* out_size, int32_t* out_first_position,
+                               int32_t* out_cursor);
+/* visited: feeds ids[0..count) one by one to a table of `entries` slots (a power of two in 64..32768) sized
+ * for an index of num_nodes nodes; out_seen[i] = 1 when the table reported ids[i] as already seen. */
+int cuhnsw_selftest_visited(int32_t entries, int64_t num_nodes, const int32_t* ids, int32_t count, int32_t* out_seen);
 
 #ifdef __cplusplus
 }

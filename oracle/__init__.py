@@ -109,7 +109,7 @@ def build_graph(vec, levels, max_m, max_m0, dist_type, ef_construction, heuristi
   schedule; any other value mirrors the batch schedule of the CUDA build."""
   g = Graph(vec, levels, max_m, max_m0, dist_type)
   ml, ep = ctypes.c_int(0), ctypes.c_int(0)
-  counters = np.zeros(2, np.int64)
+  counters = np.zeros(3, np.int64)  # distance evaluations, adjacency rows touched, bytes of those rows
   rc = _load(native).oracle_build(
     g.n, g.d, DIST[dist_type], g.vec, g.levels, g.max_m, g.max_m0, int(ef_construction), float(heuristic_coef),
     int(bool(save_remains)), int(bmax), int(ramp_div), g.rows0, g.deg0, g.dist0, g.upper_base, g.rowsU, g.degU,

@@ -5,7 +5,7 @@
 # Output stays out of git (oracle/_ref/ is ignored) but travels to the GPU box.
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
-REF="${REFERENCE_ROOT:-/root/reference}"
+REF="${REFERENCE_ROOT:-$HERE/../../reference}"  # default: a checkout named "reference" beside this repository
 SPDLOG="$(python - <<'PY'
 import os, importlib.util
 spec = importlib.util.find_spec("flashinfer")

@@ -447,7 +447,7 @@ int oracle_search(int64_t n, int d, int dist_type, const float *vec, int max_m, 
  * newcomer pass untested, the newcomer gets the full test, later candidates
  * are tested against the newcomer only (cuda_build_kernels.cuh:99-160). */
 static int select_neighbors(const graph_t *g, const uint64_t *cands, int ncands, int m, double heuristic_coef,
-                            int save_remains, int new_comer, int *out_ids, float *out_dist) {
+                            int save_remains, int new_comer, int *out_ids, float *out_dist, int64_t *evals) {
   int head = 0;
   int tail = m - 1;
   if (tail > ncands - 1) tail = ncands - 1;
@@ -469,10 +469,12 @@ static int select_neighbors(const graph_t *g, const uint64_t *cands, int ncands,
     const float *cv = g->vec + (size_t)cid * g->d;
     if (new_comer >= 0 && new_comer_inserted) {
       float dd = gdist(g, cv, new_comer);
+      *evals += 1;
       skip = cd > dd;
     } else {
       for (int k = 0; k < head; ++k) {
         float dd = gdist(g, cv, out_ids[k]);
+        *evals += 1;
         if (cd > dd) { skip = 1; break; }
       }
     }
@@ -556,10 +558,14 @@ int oracle_build(int64_t n, int d, int dist_type, const float *vec, const int *l
   int *st_deg = (int *)malloc(sizeof(int) * (size_t)cap);
   proposal_t *props = (proposal_t *)malloc(sizeof(proposal_t) * (size_t)cap * mmax);
   int64_t *seg = (int64_t *)malloc(sizeof(int64_t) * ((size_t)cap * mmax + 1));
-  int64_t c_evals = 0, c_rows = 0;
+  /* work counters: rows gathered for a distance (descent, beam search, neighbour selection with its early
+   * exit), adjacency rows read or written, and the bytes of those rows (ids + stored distances + degree:
+   * 8 * (1 + link budget of the level) each) */
+  int64_t c_evals = 0, c_rows = 0, c_row_bytes = 0;
 
   for (int l = max_level; l >= 0; --l) {
     const int m = level_stride(&g, l);
+    const int64_t rows_before = c_rows;
     int64_t nl = 0, upper_cnt = 0;
     for (int64_t i = 0; i < n; ++i)
       if (levels[i] >= l) {
@@ -570,12 +576,13 @@ int oracle_build(int64_t n, int d, int dist_type, const float *vec, const int *l
      * their finished row from there (with its distances); every other node
      * gets one edge to the node a greedy descent from the enter point
      * reaches on the level above. */
-#pragma omp parallel for schedule(dynamic, 64) num_threads(nthreads) reduction(+ : c_evals)
+#pragma omp parallel for schedule(dynamic, 64) num_threads(nthreads) reduction(+ : c_evals, c_rows)
     for (int64_t t = 0; t < nl; ++t) {
       int i = nodes[t];
       int *ids = row_ids(&g, i, l);
       float *ds = row_dist(&g, i, l);
       went[i] = 0;
+      c_rows += 1 + (levels[i] > l);  /* the initial row is written; a copied-down row is also read */
       if (levels[i] > l) {
         const int *uids = row_ids(&g, i, l + 1);
         const float *uds = row_dist(&g, i, l + 1);
@@ -647,7 +654,7 @@ int oracle_build(int64_t n, int d, int dist_type, const float *vec, const int *l
         beam_layer(&g, q, l, efc, sc, &ncand, &nres, s, &ev, &ex);
         int total = drain_sorted(sc->res, nres, sorted[tid]);
         st_deg[t] = select_neighbors(&g, sorted[tid], total, m, heuristic_coef, save_remains, -1,
-                                     st_ids + (size_t)t * m, st_dist + (size_t)t * m);
+                                     st_ids + (size_t)t * m, st_dist + (size_t)t * m, &ev);
         c_evals += ev;
         c_rows += ex + 1;
       }
@@ -674,7 +681,7 @@ int oracle_build(int64_t n, int d, int dist_type, const float *vec, const int *l
       seg[nseg] = np;
       /* phase C: per target node, newcomers in ascending source order
        * (cuda_build_kernels.cuh:295-332) */
-#pragma omp parallel for schedule(dynamic, 16) num_threads(nthreads) reduction(+ : c_rows)
+#pragma omp parallel for schedule(dynamic, 16) num_threads(nthreads) reduction(+ : c_rows, c_evals)
       for (int64_t si = 0; si < nseg; ++si) {
         int dst = (int)(props[seg[si]].key >> 32);
         int *ids = row_ids(&g, dst, l);
@@ -703,7 +710,9 @@ int oracle_build(int64_t n, int d, int dist_type, const float *vec, const int *l
           }
           if (nc > efc) nc = efc;
           int new_comer = (!save_remains && went[dst]) ? s : -1;
-          int ndeg = select_neighbors(&g, ck, nc, m, heuristic_coef, save_remains, new_comer, tmp_ids, tmp_ds);
+          int64_t sev = 0;
+          int ndeg = select_neighbors(&g, ck, nc, m, heuristic_coef, save_remains, new_comer, tmp_ids, tmp_ds, &sev);
+          c_evals += sev;
           for (int j = 0; j < ndeg; ++j) { ids[j] = tmp_ids[j]; ds[j] = tmp_ds[j]; }
           *pdeg = ndeg;
           went[dst] = 1;
@@ -712,8 +721,9 @@ int oracle_build(int64_t n, int d, int dist_type, const float *vec, const int *l
       }
       p += b;
     }
+    c_row_bytes += (c_rows - rows_before) * 8 * (1 + (int64_t)m);
   }
-  if (build_counters) { build_counters[0] = c_evals; build_counters[1] = c_rows; }
+  if (build_counters) { build_counters[0] = c_evals; build_counters[1] = c_rows; build_counters[2] = c_row_bytes; }
   for (int t = 0; t < nthreads; ++t) { scratch_free(&scs[t]); free(sorted[t]); }
   free(scs); free(sorted); free(nodes); free(went); free(st_ids); free(st_dist); free(st_deg);
   free(props); free(seg);

@@ -54,3 +54,14 @@ def engine_options(opt, **extra):
 def assert_same_bits(a, b):
   assert a.shape == b.shape
   assert (np.ascontiguousarray(a).view(np.uint32) == np.ascontiguousarray(b).view(np.uint32)).all()
+
+
+def oracle_graph_of(engine, base, opt):
+  """The engine's device-resident graph as an oracle graph over the same vectors."""
+  import oracle
+  levels, rows0, rows_u = engine.obj.get_graph()
+  g = oracle.Graph(base, levels, opt["max_m"], opt["max_m0"], opt["dist_type"])
+  g.rows0[:], g.deg0[:] = rows0, (rows0 >= 0).sum(1)
+  nu = g.rowsU.shape[0]
+  g.rowsU[:], g.degU[:] = rows_u[:nu], (rows_u[:nu] >= 0).sum(1)
+  return g

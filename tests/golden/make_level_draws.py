@@ -49,7 +49,9 @@ class _Self:
 
 
 def main():
-  ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+  ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT")
+  if not ref_root:
+    raise SystemExit("usage: make_level_draws.py <path of the reference checkout>  (or set REFERENCE_ROOT)")
   fn = reference_function(ref_root)
   out = []
   for n, seed, mult in CASES:

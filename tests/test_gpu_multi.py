@@ -46,6 +46,14 @@ def _worker(rank, world, port, out_dir):
   ids, _, _ = rep.search_knn(q[lo:hi], 10, 128)
   parts = multi.gather_rows(torch.from_numpy(ids).to(dev), world)
   split_ids = torch.cat(parts).cpu().numpy()
+  # the same split on the device: slices searched in place, gathered straight into the result (equal and
+  # ragged slice lengths)
+  rep.obj.set_stream(torch.cuda.current_stream().cuda_stream)
+  splitter = multi.SplitSearcher(multi.engine_search_into(rep.obj), rank, world)
+  qd_all = torch.from_numpy(q).to(dev)
+  even = [t.cpu().numpy() for t in splitter.search(qd_all, 10, 128)]
+  ragged = [t.cpu().numpy() for t in splitter.search(qd_all[:333], 10, 128)]
+  rep.obj.set_stream(0)
   # (b) shard per GPU, all queries everywhere, all-gather + merge on the device
   slo, shi = multi.split_range(len(base), world, rank)
   shard = CuHNSW(opt)
@@ -65,9 +73,18 @@ def _worker(rank, world, port, out_dir):
   searcher = multi.ShardedSearcher(local_search, slo, rank, world, device_merge=multi.device_merge)
   mids, md, mfound = searcher.search(q, 10, shi - slo)  # ef = shard size: every shard answers exactly
   torch.cuda.synchronize()
+  # zero-copy form: the search writes into the exchange buffer, one all-gather, merge reads it in place
+  direct = multi.ShardedSearcher(None, slo, rank, world, local_search_into=multi.engine_search_into(shard.obj))
+  dids, dd, dfound = direct.search(qd, 10, shi - slo, timed=True)
+  torch.cuda.synchronize()
+  assert direct.last_exchange_events[0].elapsed_time(direct.last_exchange_events[2]) > 0
   if rank == 0:
     single, _, _ = rep.search_knn(q, 10, 128)
+    single_all = rep.search_knn(q, 10, 128)
     np.savez(os.path.join(out_dir, "out.npz"), split_ids=split_ids, single=single, mids=mids.cpu().numpy(),
+             dids=dids.cpu().numpy(), dd=dd.cpu().numpy(), dfound=dfound.cpu().numpy(),
+             even_ids=even[0], even_dist=even[1], even_found=even[2], ragged_ids=ragged[0],
+             single_dist=single_all[1],
              md=md.cpu().numpy(), mfound=mfound.cpu().numpy(),
              exact=ds.ground_truth(base, q, 10, "dot", device=dev))
   dist.barrier()
@@ -80,6 +97,12 @@ def test_two_gpus_query_split_and_sharded_merge(tmp_path):
   mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
   z = np.load(tmp_path / "out.npz")
   assert (z["split_ids"] == z["single"]).all()
+  assert (z["even_ids"] == z["single"]).all() and (z["even_found"] == 10).all()
+  assert (z["even_dist"].view(np.uint32) == z["single_dist"].view(np.uint32)).all()
+  assert (z["ragged_ids"] == z["single"][:333]).all()
+  # both forms of the sharded exchange give the same rows
+  assert (z["dids"] == z["mids"]).all() and (z["dfound"] == z["mfound"]).all()
+  assert (z["dd"].view(np.uint32) == z["md"].view(np.uint32)).all()
   assert (z["mfound"] == 10).all() and (np.diff(z["md"], axis=1) >= 0).all()
   # exact per-shard answers merged by (distance, id) = brute force (up to fp32 matmul ties in the harness)
   agree = (z["mids"] == z["exact"]).all(axis=1).mean()

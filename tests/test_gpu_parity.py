@@ -185,6 +185,13 @@ def test_search_edge_cases(tmp_path):
   assert ids.shape == (0, 10)
   with pytest.raises(RuntimeError, match="8192"):
     eng.search_knn(q[:2], 10, 10000)
+  # queries narrower or wider than the index are refused before the engine reads them
+  for bad in (np.zeros((2, 49), np.float32), np.zeros(51, np.float32)):
+    with pytest.raises(RuntimeError, match="dimensions"):
+      eng.search_knn(bad, 10, 40)
+    with pytest.raises(RuntimeError, match="dimensions"):
+      eng.obj.search_knn_noalloc(bad, 10, 40, np.zeros((2, 10), np.int32), np.zeros((2, 10), np.float32),
+                                 np.zeros(2, np.int32))
 
 
 def test_user_visited_table_size_does_not_change_results(tmp_path):
@@ -390,6 +397,18 @@ def test_half_rows_degenerate_shapes():
   empty.build()
   ids, dist, found = empty.search_knn(np.zeros((3, 8), np.float32), 5, 10)
   assert (found == 0).all() and (ids == -1).all()
+  # empty slots read +inf, bit for bit, from every entry point
+  inf_bits = np.full((3, 5), 0x7f800000, np.uint32)
+  assert (dist.view(np.uint32) == inf_bits).all()
+  out = (np.zeros((3, 5), np.int32), np.zeros((3, 5), np.float32), np.ones(3, np.int32))
+  empty.obj.search_knn_noalloc(np.zeros((3, 8), np.float32), 5, 10, *out)
+  assert (out[1].view(np.uint32) == inf_bits).all() and (out[0] == -1).all() and (out[2] == 0).all()
+  import torch
+  dev = [torch.zeros((3, 8), device="cuda"), torch.zeros((3, 5), dtype=torch.int32, device="cuda"),
+         torch.zeros((3, 5), device="cuda"), torch.ones(3, dtype=torch.int32, device="cuda")]
+  empty.obj.search_knn_device(dev[0].data_ptr(), 3, 5, 10, dev[1].data_ptr(), dev[2].data_ptr(), dev[3].data_ptr())
+  empty.obj.synchronize()
+  assert (dev[2].cpu().numpy().view(np.uint32) == inf_bits).all() and (dev[1].cpu().numpy() == -1).all()
 
 
 def test_half_rows_keep_recall():
@@ -499,6 +518,19 @@ def test_sharded_search_with_device_merge_equals_exact_answer():
   assert_same_bits(out_d.cpu().numpy(), host_d)
   exact, _ = oracle.bruteforce(base, q, 10, "dot")
   assert (out_ids.cpu().numpy() == exact).all()  # ef = shard size makes every shard exact
+  # the same merge reading the [parts, 2, nq, k] buffer an all-gather fills, shard-local ids + offsets
+  from cuhnsw_b200.cuhnsw_bind import load_library
+  local_ids = [torch.where(b >= 0, b - multi.split_range(len(base), parts, r)[0], b) for r, b in enumerate(ids_blocks)]
+  gathered = torch.stack([torch.stack([i, d.view(torch.int32)]) for i, d in zip(local_ids, dist_blocks)]).contiguous()
+  offsets = torch.tensor([multi.split_range(len(base), parts, r)[0] for r in range(parts)], dtype=torch.int32,
+                         device="cuda")
+  g_ids, g_d, g_found = torch.empty_like(out_ids), torch.empty_like(out_d), torch.empty_like(found)
+  rc = load_library().cuhnsw_merge_topk_gathered_device(
+    gathered.data_ptr(), offsets.data_ptr(), parts, len(q), 10, g_ids.data_ptr(), g_d.data_ptr(), g_found.data_ptr(),
+    torch.cuda.current_stream().cuda_stream)
+  torch.cuda.synchronize()
+  assert rc == 0 and (g_ids == out_ids).all() and (g_found == found).all()
+  assert_same_bits(g_d.cpu().numpy(), out_d.cpu().numpy())
 
 
 # ---------------------------------------------------------------- full size, size-independent properties

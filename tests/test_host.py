@@ -56,7 +56,9 @@ def test_init_error_behaviour_matches_reference_binding():
     b = CuHNSWBind()
     assert b.init(os.path.join(tmp, "missing.json")) is False
     assert b.init(write_opt(tmp, "{not json")) is False
-    assert b.init(write_opt(tmp, '{"a": [1, 2]}')) is False
+    assert b.init(write_opt(tmp, '{"a": {"b": 1}}')) is False
+    assert b.init(write_opt(tmp, '{"a": [1, [2]]}')) is False
+    assert b.init(write_opt(tmp, '{"a": [1, "x"]}')) is False
     with pytest.raises(RuntimeError, match="invalid dist type hamming"):
       b.init(write_opt(tmp, {"dist_type": "hamming"}))
     with pytest.raises(RuntimeError, match="max_m"):
@@ -89,6 +91,20 @@ def test_call_order_and_argument_checks():
       b.search_knn(q, 3, 10, nns, np.zeros((1, 3), np.float32), np.zeros(1, np.int32))
     with pytest.raises(RuntimeError, match="float32"):
       b.search_knn(q, 3, 10, nns, np.zeros((1, 3), np.float64), np.zeros(1, np.int32))
+    # both host-buffer searches check their output arrays before anything is written through them
+    for search in (b.search_knn, b.search_knn_noalloc):
+      with pytest.raises(RuntimeError, match="float32"):
+        search(q, 3, 10, nns, np.zeros((1, 3), np.float64), np.zeros(1, np.int32))
+      with pytest.raises(RuntimeError, match="too small"):
+        search(q, 3, 10, np.zeros((1, 2), np.int32), np.zeros((1, 3), np.float32), np.zeros(1, np.int32))
+      with pytest.raises(RuntimeError, match="int32"):
+        search(q, 3, 10, nns, np.zeros((1, 3), np.float32), np.zeros(1, np.int64))
+      with pytest.raises(RuntimeError, match="writable"):
+        ro = np.zeros((1, 3), np.float32)
+        ro.flags.writeable = False
+        search(q, 3, 10, nns, ro, np.zeros(1, np.int32))
+      with pytest.raises(RuntimeError, match="topk"):
+        search(q, 0, 10, nns, np.zeros((1, 3), np.float32), np.zeros(1, np.int32))
     with pytest.raises(RuntimeError, match="cannot open"):
       b.load_index(os.path.join(tmp, "nope.index"))
     short = os.path.join(tmp, "short.index")
@@ -136,6 +152,9 @@ def test_extension_options_and_their_validation():
   proto = aux.get_opt_as_proto({})
   assert (proto.batch_max, proto.ramp_div, proto.device_id) == (0, 4, -1)
   assert (proto.search_team, proto.search_schedule, proto.row_dtype) == (-1, True, "f32")
+  assert proto.devices == [] and aux.proto_to_dict(aux.get_opt_as_proto({"devices": [0, 1]}))["devices"] == [0, 1]
+  with pytest.raises(TypeError):
+    aux.get_opt_as_proto({"devices": "0,1"})
   d = aux.proto_to_dict(aux.get_opt_as_proto({"row_dtype": "f16", "search_schedule": False, "search_team": 1}))
   assert d["row_dtype"] == "f16" and d["search_schedule"] is False and d["search_team"] == 1
   with pytest.raises(TypeError):
@@ -143,6 +162,12 @@ def test_extension_options_and_their_validation():
   with tempfile.TemporaryDirectory() as tmp:
     b = CuHNSWBind()
     assert b.init(write_opt(tmp, {"row_dtype": "f16", "search_schedule": False}))
+    assert b.init(write_opt(tmp, {"devices": [0, 1, 1]}))
+    assert b.init(write_opt(tmp, {"devices": []}))
+    with pytest.raises(RuntimeError, match="devices"):
+      b.init(write_opt(tmp, {"devices": [0, -1]}))
+    with pytest.raises(RuntimeError, match="disagree"):
+      b.init(write_opt(tmp, {"devices": [1, 0], "device_id": 0}))
     with pytest.raises(RuntimeError, match="row_dtype must be f32 or f16"):
       CuHNSWBind().init(write_opt(tmp, {"row_dtype": "bf16"}))
 

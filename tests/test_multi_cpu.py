@@ -54,6 +54,18 @@ def _worker(rank, world, port, out_dir):
   parts = [t.numpy() for t in multi.gather_rows(padded, world)]
   split_ids = np.concatenate([p[:multi.split_range(len(q), world, r)[1] - multi.split_range(len(q), world, r)[0]]
                               for r, p in enumerate(parts)])
+  # the same through SplitSearcher (what the benchmark's strong-scaling block uses), equal and ragged slices
+  import torch
+
+  def search_into(qq, k, ef, out_ids, out_dist, out_found):
+    a, b, c = oracle.search(g, qq.numpy(), k, ef)
+    out_ids.copy_(torch.from_numpy(a))
+    out_dist.copy_(torch.from_numpy(b))
+    out_found.copy_(torch.from_numpy(c))
+
+  splitter = multi.SplitSearcher(search_into, rank, world)
+  even = splitter.search(torch.from_numpy(q), 10, 40)
+  ragged = splitter.search(torch.from_numpy(q[:117]), 10, 40)
   # (b) base set sharded, all queries on every rank, all-gather + merge
   slo, shi = multi.split_range(len(base), world, rank)
   shard = base[slo:shi]
@@ -63,7 +75,10 @@ def _worker(rank, world, port, out_dir):
   mids, md, mfound = searcher.search(q, 10, len(shard))  # ef = shard size: every shard answers exactly
   if rank == 0:
     np.savez(os.path.join(out_dir, "out.npz"), split_ids=split_ids, single_ids=oracle.search(g, q, 10, 40)[0],
-             mids=mids, md=md, mfound=mfound, exact=oracle.bruteforce(base, q, 10, "dot")[0])
+             mids=mids, md=md, mfound=mfound, exact=oracle.bruteforce(base, q, 10, "dot")[0],
+             even_ids=even[0].numpy(), even_dist=even[1].numpy(), even_found=even[2].numpy(),
+             ragged_ids=ragged[0].numpy(), ragged_found=ragged[2].numpy(),
+             single_dist=oracle.search(g, q, 10, 40)[1])
   dist.barrier()
   dist.destroy_process_group()
 
@@ -75,6 +90,9 @@ def test_two_ranks_query_split_and_sharded_merge(tmp_path):
   z = np.load(tmp_path / "out.npz")
   # query split over a replica = the single-process answer, row for row
   assert (z["split_ids"] == z["single_ids"]).all()
+  assert (z["even_ids"] == z["single_ids"]).all() and (z["even_found"] == 10).all()
+  assert (z["even_dist"].view(np.uint32) == z["single_dist"].view(np.uint32)).all()
+  assert (z["ragged_ids"] == z["single_ids"][:117]).all() and (z["ragged_found"] == 10).all()
   # exact per-shard answers merged by (distance, id) = exact global answer
   assert (z["mids"] == z["exact"]).all() and (z["mfound"] == 10).all()
   assert (np.diff(z["md"], axis=1) >= 0).all()

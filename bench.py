@@ -240,6 +240,14 @@ def native_oracle():
     return False
 
 
+def truth_device():
+  try:
+    import torch
+    return "cuda" if torch.cuda.is_available() else "cpu"
+  except Exception:  # pylint: disable=broad-except
+    return "cpu"
+
+
 def sweep_until_target(search_ids, truth, sweep, extra):
   """recall at every ef of the sweep; when the sweep ends below the target, the extra values in turn."""
   from cuhnsw_b200 import datasets as ds
@@ -278,7 +286,9 @@ def run_reference(args, rank, world):
                          0.25, False, bmax=DEFAULT_BATCH_MAX, ramp_div=DEFAULT_RAMP_DIV, nthreads=threads, native=native)
   build_s = time.perf_counter() - t0
   nr = min(nq, args.recall_queries)
-  truth = ds.ground_truth(base, queries[:nr], topk, opt["dist_type"])
+  # exact answer computed the way the GPU arm computes it (same matmul, same device when one is present), so
+  # that both arms score their recall against the very same truth
+  truth = ds.ground_truth(base, queries[:nr], topk, opt["dist_type"], device=truth_device())
   recalls = sweep_until_target(lambda ef: oracle.search(g, queries[:nr], topk, ef, nthreads=threads, native=native)[0],
                                truth, spec["ef_sweep"], args.ef_extra)
   ef = pick_ef(recalls)

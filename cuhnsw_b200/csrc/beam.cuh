@@ -20,7 +20,7 @@
 namespace hnsw {
 
 __device__ __forceinline__ VecTable make_table(const GraphView& g) {
-  return VecTable{static_cast<const unsigned char*>(g.vec), (size_t)g.vstride * (g.f16 ? 2 : 4), (g.d + 3) / 4, g.d,
+  return VecTable{static_cast<const unsigned char*>(g.vec), (size_t)g.vstride * (g.rows16 ? 2 : 4), (g.d + 3) / 4, g.d,
                   g.dist_type};
 }
 

@@ -496,15 +496,17 @@ static cudaError_t build_batch_rows(const BuildLevel& L, const BuildScratch& S, 
 
 cudaError_t launch_init_level(const BuildLevel& L, unsigned long long* ticket, int sm_count, cudaStream_t stream) {
   if (L.n_level <= 0) return cudaSuccess;
-  return L.g.f16 ? init_level_rows<RowF16>(L, ticket, sm_count, stream)
-                 : init_level_rows<RowF32>(L, ticket, sm_count, stream);
+#define CALL(R) init_level_rows<R>(L, ticket, sm_count, stream)
+  return HNSW_WITH_ROWS(L.g.rows16, CALL);
+#undef CALL
 }
 
 cudaError_t launch_build_batch(const BuildLevel& L, const BuildScratch& S, long long first, int count,
                                int sm_count, cudaStream_t stream) {
   if (count <= 0) return cudaSuccess;
-  return L.g.f16 ? build_batch_rows<RowF16>(L, S, first, count, sm_count, stream)
-                 : build_batch_rows<RowF32>(L, S, first, count, sm_count, stream);
+#define CALL(R) build_batch_rows<R>(L, S, first, count, sm_count, stream)
+  return HNSW_WITH_ROWS(L.g.rows16, CALL);
+#undef CALL
 }
 
 // ---------------------------------------------------------------------------
@@ -530,23 +532,33 @@ __global__ void unpad_rows_kernel(const float* src, float* dst, long long n, int
 }
 // half rows: rounded to nearest even and stored in the paired-column layout of RowF16 (the rows were
 // cleared beforehand, so the padding reads zero)
-__global__ void pad_rows_f16_kernel(const float* src, long long src_stride, __half* dst, long long n, int d,
-                                    int vstride) {
+template <class H>
+__device__ __forceinline__ H round16(float x);
+template <>
+__device__ __forceinline__ __half round16<__half>(float x) { return __float2half_rn(x); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 round16<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+__device__ __forceinline__ float widen16(__half x) { return __half2float(x); }
+__device__ __forceinline__ float widen16(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <class H>
+__global__ void pad_rows_16_kernel(const float* src, long long src_stride, H* dst, long long n, int d, int vstride) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long total = n * d;
   for (; idx < total; idx += (long long)gridDim.x * blockDim.x) {
     long long r = idx / d;
     int e = (int)(idx % d);
-    dst[r * vstride + RowF16::position(d, e)] = __float2half_rn(src[r * src_stride + e]);
+    dst[r * vstride + RowF16::position(d, e)] = round16<H>(src[r * src_stride + e]);
   }
 }
-__global__ void unpad_rows_f16_kernel(const __half* src, float* dst, long long n, int d, int vstride) {
+template <class H>
+__global__ void unpad_rows_16_kernel(const H* src, float* dst, long long n, int d, int vstride) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long total = n * d;
   for (; idx < total; idx += (long long)gridDim.x * blockDim.x) {
     long long r = idx / d;
     int e = (int)(idx % d);
-    dst[idx] = __half2float(src[r * vstride + RowF16::position(d, e)]);
+    dst[idx] = widen16(src[r * vstride + RowF16::position(d, e)]);
   }
 }
 __global__ void unpack_links_kernel(const unsigned* __restrict__ records, long long rec_words, long long count,
@@ -564,7 +576,9 @@ __global__ void unpack_links_kernel(const unsigned* __restrict__ records, long l
       atomicMin(bad, (unsigned long long)(first + r + 1));
     } else if ((unsigned)j < deg) {
       const unsigned v = rec[1 + j];
-      if ((long long)v >= n) atomicMin(bad, (unsigned long long)(first + r + 1));
+      bool twice = false;  // an id listed twice in one row would reach the list merge as two equal newcomers
+      for (int k = 0; k < j; ++k) twice = twice || rec[1 + k] == v;
+      if ((long long)v >= n || twice) atomicMin(bad, (unsigned long long)(first + r + 1));
       else id = (int)v;
     }
     rows[idx] = id;
@@ -583,13 +597,17 @@ static unsigned blocks_for(long long total) {
   return (unsigned)b;
 }
 cudaError_t launch_pad_rows(const float* src, long long src_stride, void* dst, long long n, int d, int vstride,
-                            int f16, cudaStream_t stream) {
+                            int rows16, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
-  if (f16) {
-    cudaError_t e = cudaMemsetAsync(dst, 0, (size_t)n * vstride * sizeof(__half), stream);
+  if (rows16) {
+    cudaError_t e = cudaMemsetAsync(dst, 0, (size_t)n * vstride * 2, stream);
     if (e != cudaSuccess) return e;
-    pad_rows_f16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(src, src_stride, static_cast<__half*>(dst), n, d,
-                                                               vstride);
+    if (rows16 == kRowsBF16)
+      pad_rows_16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(src, src_stride, static_cast<__nv_bfloat16*>(dst), n, d,
+                                                                vstride);
+    else
+      pad_rows_16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(src, src_stride, static_cast<__half*>(dst), n, d,
+                                                                vstride);
   } else {
     pad_rows_kernel<<<blocks_for(n * vstride), 256, 0, stream>>>(src, src_stride, static_cast<float*>(dst), n, d,
                                                                  vstride);
@@ -604,11 +622,14 @@ cudaError_t launch_unpack_links(const unsigned* records, long long rec_words, lo
                                                                       rows, stride, labels, bad);
   return cudaGetLastError();
 }
-cudaError_t launch_unpad_rows(const void* src, float* dst, long long n, int d, int vstride, int f16,
+cudaError_t launch_unpad_rows(const void* src, float* dst, long long n, int d, int vstride, int rows16,
                               cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
-  if (f16)
-    unpad_rows_f16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(static_cast<const __half*>(src), dst, n, d, vstride);
+  if (rows16 == kRowsBF16)
+    unpad_rows_16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), dst, n, d,
+                                                                vstride);
+  else if (rows16)
+    unpad_rows_16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(static_cast<const __half*>(src), dst, n, d, vstride);
   else
     unpad_rows_kernel<<<blocks_for(n * d), 256, 0, stream>>>(static_cast<const float*>(src), dst, n, d, vstride);
   return cudaGetLastError();

@@ -51,13 +51,14 @@ static cudaError_t batch_distance_rows(const GraphView& g, const int* src, const
   return batch_distance_t<typename E::Wide>(g, src, dst, npairs, out, stream);
 }
 
-int row_stride_elements(int d, int f16) { return f16 ? RowF16::stride(d) : RowF32::stride(d); }
+int row_stride_elements(int d, int rows16) { return rows16 ? RowF16::stride(d) : RowF32::stride(d); }
 
 cudaError_t launch_batch_distance(const GraphView& g, const int* src, const int* dst, long long npairs, float* out,
                                   cudaStream_t stream) {
   if (npairs <= 0) return cudaSuccess;
-  return g.f16 ? batch_distance_rows<RowF16>(g, src, dst, npairs, out, stream)
-               : batch_distance_rows<RowF32>(g, src, dst, npairs, out, stream);
+#define CALL(R) batch_distance_rows<R>(g, src, dst, npairs, out, stream)
+  return HNSW_WITH_ROWS(g.rows16, CALL);
+#undef CALL
 }
 
 }  // namespace hnsw

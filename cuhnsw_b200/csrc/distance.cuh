@@ -13,13 +13,14 @@
 //
 // fp32 rows are stored in element order, padded with zeros to a multiple of 8 floats (32-byte sectors).
 //
-// fp16 rows (IEEE half, round to nearest even of the input) keep the same lanes, accumulators and order of
+// 16-bit rows (IEEE half or bfloat16, round to nearest even of the input) keep the same lanes, accumulators and order of
 // additions, so they give exactly the canonical fp32 distance over the rounded values; only the layout
 // differs, so that a lane still loads 16 bytes at a time: a chunk is four consecutive elements, a lane owns
 // chunk columns c = 0, 1, 2, ... (chunk number lane + T*c), and the 8 halves of its columns 2p and 2p + 1
 // are stored side by side at 16-byte slot p*T + lane of the row.  Rows are padded with zeros to whole pairs
 // of columns (T*16 bytes).
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -50,7 +51,14 @@ struct RowF32 {
     }
   }
 };
-struct RowF16 {
+// two packed 16-bit values -> two floats
+template <bool kBf16>
+__device__ __forceinline__ float2 unpack2(unsigned w) {
+  if (kBf16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));  // a bfloat16 is the upper half of a float
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+template <bool kBf16>
+struct Row16 {
   __host__ __device__ static int team(int d) { return d <= 128 ? 8 : 32; }
   __host__ __device__ static int stride(int d) {
     const int t = team(d), nchunk = (d + 3) / 4;
@@ -69,17 +77,24 @@ struct RowF16 {
       const int p = (c0 >> 1) + jj;
       uint4 u = make_uint4(0u, 0u, 0u, 0u);
       if (kInner || p < npair) u = __ldg(reinterpret_cast<const uint4*>(row) + p * T + lane);
-      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
-      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+      const float2 a = unpack2<kBf16>(u.x);
+      const float2 b = unpack2<kBf16>(u.y);
       v[2 * jj] = make_float4(a.x, a.y, b.x, b.y);
       if (2 * jj + 1 < N) {
-        const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&u.z));
-        const float2 e = __half22float2(*reinterpret_cast<const __half2*>(&u.w));
+        const float2 c = unpack2<kBf16>(u.z);
+        const float2 e = unpack2<kBf16>(u.w);
         v[2 * jj + 1] = make_float4(c.x, c.y, e.x, e.y);
       }
     }
   }
 };
+using RowF16 = Row16<false>;
+using RowBF16 = Row16<true>;
+// row storage of an index: GraphView::rows16
+constexpr int kRowsF32 = 0, kRowsF16 = 1, kRowsBF16 = 2;
+// CALL(Row) with the row type that `kind` names
+#define HNSW_WITH_ROWS(kind, CALL) \
+  ((kind) == ::hnsw::kRowsF16 ? CALL(::hnsw::RowF16) : (kind) == ::hnsw::kRowsBF16 ? CALL(::hnsw::RowBF16) : CALL(::hnsw::RowF32))
 
 __device__ __forceinline__ void fma4(float4& acc, const float4& a, const float4& b, int dist_type) {
   if (dist_type == DIST_DOT) {

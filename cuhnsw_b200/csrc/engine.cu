@@ -129,7 +129,8 @@ int Engine::Init(const char* opt_path, int device_override) {
   o.search_team = (int)js.number("search_team", o.search_team);
   o.search_schedule = js.boolean("search_schedule", o.search_schedule);
   o.row_dtype = js.string("row_dtype", o.row_dtype);
-  if (o.row_dtype != "f32" && o.row_dtype != "f16") return Fail(kInvalidArgument, "row_dtype must be f32 or f16");
+  if (o.row_dtype != "f32" && o.row_dtype != "f16" && o.row_dtype != "bf16")
+    return Fail(kInvalidArgument, "row_dtype must be f32, f16 or bf16");
   // the reference's schema spells it heuristic_coef, its README heuristic_coff
   o.heuristic_coef = js.number("heuristic_coef", js.number("heuristic_coff", o.heuristic_coef));
   o.batch_max = (long long)js.number("batch_max", (double)o.batch_max);
@@ -192,11 +193,11 @@ int Engine::SetData(const float* data, long long num_data, int num_dims) {
     long long r = std::min(rows_per_chunk, n_ - s);
     CU(cudaMemcpyAsync(raw.get(), data + (size_t)s * num_dims, (size_t)r * num_dims * sizeof(float),
                        cudaMemcpyHostToDevice, stream_));
-    CU(launch_pad_rows(raw.get(), num_dims, RowPtr(s), r, num_dims, vstride_, f16_ ? 1 : 0, stream_));
+    CU(launch_pad_rows(raw.get(), num_dims, RowPtr(s), r, num_dims, vstride_, rows16_, stream_));
     CU(cudaStreamSynchronize(stream_));
   }
   has_data_ = true;
-  Log(3, "copied data (%lld x %d), row stride %d %s", n_, d_, vstride_, f16_ ? "halves" : "floats");
+  Log(3, "copied data (%lld x %d), row stride %d %s", n_, d_, vstride_, rows16_ ? "16-bit values" : "floats");
   return kOk;
 }
 
@@ -206,12 +207,12 @@ int Engine::AllocRows(long long num_data, int num_dims) {
   if (rc) return rc;
   n_ = num_data;
   d_ = num_dims;
-  f16_ = opt_.row_dtype == "f16";
-  vstride_ = row_stride_elements(num_dims, f16_ ? 1 : 0);  // rows start on 32-byte sectors
+  rows16_ = opt_.row_dtype == "f16" ? 1 : opt_.row_dtype == "bf16" ? 2 : 0;
+  vstride_ = row_stride_elements(num_dims, rows16_);  // rows start on 32-byte sectors
   has_data_ = has_levels_ = has_graph_ = labelled_ = false;
   labels_h_.clear();
   labels_d_.release();
-  CU(vec_.alloc(((size_t)n_ * vstride_ * (f16_ ? 2 : 4) + 3) / 4));
+  CU(vec_.alloc(((size_t)n_ * vstride_ * (rows16_ ? 2 : 4) + 3) / 4));
   return kOk;
 }
 
@@ -270,7 +271,7 @@ GraphView Engine::View() const {
   GraphView g;
   g.vec = vec_.get();
   g.vstride = vstride_;
-  g.f16 = f16_ ? 1 : 0;
+  g.rows16 = rows16_;
   g.d = d_;
   g.dist_type = dist_type_;
   g.n = n_;
@@ -297,7 +298,10 @@ int Engine::ResolveVsize(int cap, long long nq, int* vsize) const {
     // 3576 evaluations per query and 5.67 ms with 2048 entries, 2099 and 4.98 ms with 16384.
     const int kind = nq < 0 ? kSearchWarp
                             : search_kernel_kind(d_, nq, opt_.search_team, opt_.reverse_cand ? 1 : 0, sm_count_);
-    const int warps = d_ <= 128 ? 32 : kind == kSearchTeam ? 4 : kind == kSearchWarpDeep ? 8 : 16;
+#ifndef HNSW_SEARCH_WARPS_SMALL
+#define HNSW_SEARCH_WARPS_SMALL 32
+#endif
+    const int warps = d_ <= 128 ? HNSW_SEARCH_WARPS_SMALL : kind == kSearchTeam ? 4 : kind == kSearchWarpDeep ? 8 : 16;
     const int top = kind == kSearchTeam ? 16384 : kind == kSearchWarpDeep ? 8192 : 4096;
     const long long budget = (long long)smem_optin_ / warps - 640;
     const int floor_entries = std::min(4096, std::max(512, next_pow2(4ll * cap)));
@@ -666,7 +670,7 @@ int Engine::SaveIndex(const char* path) {
     const long long r = std::min(chunk, n_ - s);
     CU(cudaMemcpy(rows.data(), rows0_.get() + (size_t)s * stride0_, (size_t)r * stride0_ * sizeof(int),
                   cudaMemcpyDeviceToHost));
-    CU(launch_unpad_rows(RowPtr(s), unpadded.get(), r, d_, vstride_, f16_ ? 1 : 0, stream_));
+    CU(launch_unpad_rows(RowPtr(s), unpadded.get(), r, d_, vstride_, rows16_, stream_));
     CU(cudaMemcpyAsync(vecs.data(), unpadded.get(), (size_t)r * d_ * sizeof(float), cudaMemcpyDeviceToHost, stream_));
     CU(cudaStreamSynchronize(stream_));
     std::memset(out.data(), 0, (size_t)r * rec);
@@ -784,7 +788,7 @@ int Engine::LoadIndex(const char* path) {
       CU(launch_unpack_links(raw.get(), rec_words, r, s, m0, n, rows0_.get() + (size_t)s * stride0_, stride0_,
                              labels_d_.get() + s, bad.get(), stream_));
       CU(launch_pad_rows(reinterpret_cast<const float*>(raw.get() + 1 + m0), rec_words, RowPtr(s), r, d, vstride_,
-                         f16_ ? 1 : 0, stream_));
+                         rows16_, stream_));
       for (long long i = 0; i < r; ++i) {
         uint64_t label;
         std::memcpy(&label, buf.data() + (size_t)(i + 1) * rec - 8, 8);
@@ -796,7 +800,8 @@ int Engine::LoadIndex(const char* path) {
     CU(cudaMemcpy(&first_bad, bad.get(), sizeof(first_bad), cudaMemcpyDeviceToHost));
     if (first_bad != ~0ull) {
       std::ostringstream os;
-      os << "index file: record " << (first_bad - 1) << " has a degree above maxM0 or a neighbour id out of range";
+      os << "index file: record " << (first_bad - 1)
+         << " has a degree above maxM0, a neighbour id out of range or a neighbour listed twice";
       return Fail(kParseError, os.str());
     }
   }
@@ -830,6 +835,8 @@ int Engine::LoadIndex(const char* path) {
         uint32_t id;
         std::memcpy(&id, o + 4 + 4 * (size_t)j, 4);
         if (id >= (uint64_t)n) return Fail(kParseError, "index file: bad upper-layer neighbour");
+        for (uint32_t k = 0; k < j; ++k)
+          if (rowsU[at + k] == (int)id) return Fail(kParseError, "index file: upper-layer neighbour listed twice");
         rowsU[at + j] = (int)id;
       }
     }
@@ -886,7 +893,7 @@ int Engine::CloneFrom(const Engine& src) {
   opt_.level_mult = src.opt_.level_mult;
   int rc = AllocRows(src.n_, src.d_);
   if (rc) return rc;
-  if (f16_ != src.f16_) return Fail(kBadState, "replica and source store rows in different types");
+  if (rows16_ != src.rows16_) return Fail(kBadState, "replica and source store rows in different types");
   stride0_ = src.stride0_;
   strideU_ = src.strideU_;
   max_level_ = src.max_level_;

@@ -41,7 +41,7 @@ struct Options {
   bool nrz = false;
   bool reverse_cand = false;
   int search_team = -1;  // d > 128: 1 = CTA per query, 0 = warp per query, -1 = chosen by batch size
-  std::string row_dtype = "f32";  // "f16": rows stored as IEEE half, distances in fp32 over the stored values
+  std::string row_dtype = "f32";  // "f16" / "bf16": rows stored in 16 bits, distances in fp32 over the stored values
   bool search_schedule = true;  // batches of more than one wave: serve the queries with the farthest entry first
   double heuristic_coef = 0.25;
   // extensions (absent from the reference's schema; optional keys of the option file)
@@ -145,9 +145,9 @@ class Engine {
   long long n_ = 0;
   int d_ = 0;
   int vstride_ = 0;
-  bool f16_ = false;
+  int rows16_ = 0;  // 0 fp32 rows, 1 IEEE half, 2 bfloat16
   void* RowPtr(long long row) const {
-    return reinterpret_cast<unsigned char*>(vec_.get()) + (size_t)row * vstride_ * (f16_ ? 2 : 4);
+    return reinterpret_cast<unsigned char*>(vec_.get()) + (size_t)row * vstride_ * (rows16_ ? 2 : 4);
   }
   int dist_type_ = 0;
   int stride0_ = 0, strideU_ = 0;

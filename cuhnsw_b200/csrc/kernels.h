@@ -10,8 +10,8 @@ namespace hnsw {
 struct GraphView {
   const void* vec;        // n x vstride elements, rows zero padded, 32-byte aligned rows
   int vstride;            // elements per row (row_stride_elements)
-  int f16;                // rows are stored as IEEE half (round to nearest even of the input); distances are
-                          // the fp32 distances over the stored values
+  int rows16;             // 0: fp32 rows; 1: IEEE half; 2: bfloat16 (round to nearest even of the input).  Distances
+                          // are always the fp32 distances over the stored values
   int d;
   int dist_type;          // 0 dot (-dot), 1 l2 (squared)
   long long n;
@@ -125,19 +125,20 @@ cudaError_t launch_init_level(const BuildLevel& L, unsigned long long* ticket, i
 cudaError_t launch_build_batch(const BuildLevel& L, const BuildScratch& S, long long first, int count,
                                int sm_count, cudaStream_t stream);
 // elements per stored row: d rounded up to 8 floats, or whole pairs of chunk columns of halves
-int row_stride_elements(int d, int f16);
+int row_stride_elements(int d, int rows16);
 // pads n fp32 rows of d elements (row r starts at src + r * src_stride; src_stride = d for a dense matrix,
 // the record length in words for rows embedded in index-file records) into n x vstride rows of floats or
 // halves, and back
 cudaError_t launch_pad_rows(const float* src, long long src_stride, void* dst, long long n, int d, int vstride,
-                            int f16, cudaStream_t stream);
-cudaError_t launch_unpad_rows(const void* src, float* dst, long long n, int d, int vstride, int f16,
+                            int rows16, cudaStream_t stream);
+cudaError_t launch_unpad_rows(const void* src, float* dst, long long n, int d, int vstride, int rows16,
                               cudaStream_t stream);
 cudaError_t launch_fill_i32(int* p, long long n, int v, cudaStream_t stream);
 // Level-0 records of an hnswlib index file, already on the device (`count` records of `rec_words` 32-bit words:
 // degree word, max_m0 neighbour slots, the vector, a 64-bit label): writes the -1 padded adjacency rows and
-// the labels truncated to int (cpp/src/cuhnsw_base.cu:300-324).  A degree above max_m0 or a neighbour id
-// outside [0, n) stores 1 + the record number of the first offender found in *bad (0 = file is sound).
+// the labels truncated to int (cpp/src/cuhnsw_base.cu:300-324).  A degree above max_m0, a neighbour id outside
+// [0, n) or an id listed twice in one row stores 1 + the smallest offending record number in *bad (which the
+// caller presets to all ones).
 cudaError_t launch_unpack_links(const unsigned* records, long long rec_words, long long count, long long first,
                                 int max_m0, long long n, int* rows, int stride, int* labels,
                                 unsigned long long* bad, cudaStream_t stream);

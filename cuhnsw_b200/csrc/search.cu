@@ -143,7 +143,9 @@ size_t search_schedule_tmp_bytes(long long nq) {
 cudaError_t schedule_search(SearchParams& p, const SearchSchedule& s, int sm_count, cudaStream_t stream) {
   (void)sm_count;
   if (p.nq > s.capacity || p.nq > 0x7fffffffll) return cudaErrorInvalidValue;  // the sort counts items in an int
-  cudaError_t e = p.g.f16 ? launch_entry_rows<RowF16>(p, s, stream) : launch_entry_rows<RowF32>(p, s, stream);
+#define CALL(R) launch_entry_rows<R>(p, s, stream)
+  cudaError_t e = HNSW_WITH_ROWS(p.g.rows16, CALL);
+#undef CALL
   if (e != cudaSuccess) return e;
   // the upper 16 bits of the key (sign, exponent, 7 bits of mantissa) order the queries finely enough
   size_t bytes = s.sort_tmp_bytes;
@@ -234,8 +236,9 @@ static cudaError_t launch_search_rows(const SearchParams& p, int sm_count, cudaS
 
 cudaError_t launch_search(const SearchParams& p, int sm_count, cudaStream_t stream, const SearchSchedule* sched) {
   if (p.nq <= 0) return cudaSuccess;
-  return p.g.f16 ? launch_search_rows<RowF16>(p, sm_count, stream, sched)
-                 : launch_search_rows<RowF32>(p, sm_count, stream, sched);
+#define CALL(R) launch_search_rows<R>(p, sm_count, stream, sched)
+  return HNSW_WITH_ROWS(p.g.rows16, CALL);
+#undef CALL
 }
 
 }  // namespace hnsw

@@ -137,7 +137,9 @@ cudaError_t launch_search_team(const SearchParams& p0, int sm_count, cudaStream_
   SearchParams p = p0;
   const size_t smem = search_team_smem(p.g.d, p.ef, p.vsize, p.g.n);
   p.smem_per_warp = (int)smem;
-  auto kern = p.g.f16 ? knn_search_team_kernel<Pick<RowF16>::Wide> : knn_search_team_kernel<Pick<RowF32>::Wide>;
+#define CALL(R) knn_search_team_kernel<typename Pick<R>::Wide>
+  auto kern = HNSW_WITH_ROWS(p.g.rows16, CALL);
+#undef CALL
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   int per_sm = 0;

@@ -327,21 +327,26 @@ def test_degenerate_builds():
 
 
 # ---------------------------------------------------------------- fp16 rows
-def _rounded(x):
+def _rounded(x, row_dtype="f16"):
+  if row_dtype == "bf16":
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(x)).to(torch.bfloat16).to(torch.float32).numpy()
   return x.astype(np.float16).astype(np.float32)
 
 
-@pytest.mark.parametrize("d,dist_type", [(50, "dot"), (33, "l2"), (128, "l2"), (200, "dot"), (960, "l2")])
-def test_half_rows_give_the_canonical_distance_over_the_rounded_values(d, dist_type, tmp_path):
-  """row_dtype = f16 stores round-to-nearest-even halves; every distance, and therefore every search and
-  every built graph, equals the fp32 oracle run on the rounded vectors, bit for bit."""
+@pytest.mark.parametrize("d,dist_type,row_dtype", [(50, "dot", "f16"), (33, "l2", "f16"), (128, "l2", "f16"),
+                                                   (200, "dot", "f16"), (960, "l2", "f16"), (50, "dot", "bf16"),
+                                                   (97, "l2", "bf16"), (960, "l2", "bf16")])
+def test_half_rows_give_the_canonical_distance_over_the_rounded_values(d, dist_type, row_dtype, tmp_path):
+  """row_dtype = f16 / bf16 stores round-to-nearest-even 16-bit values; every distance, and therefore every
+  search and every built graph, equals the fp32 oracle run on the rounded vectors, bit for bit."""
   rng = np.random.default_rng(77 + d)
   n = 3000
   base = (rng.standard_normal((n, d)) * (3.0 if dist_type == "l2" else 1.0)).astype(np.float32)
   q = rng.standard_normal((150, d)).astype(np.float32)
-  base_r = _rounded(base)
+  base_r = _rounded(base, row_dtype)
   opt = {"dist_type": dist_type, "max_m": 12, "max_m0": 24, "ef_construction": 80, "level_mult": 0.4, "seed": 9,
-         "row_dtype": "f16", "batch_max": 300}
+         "row_dtype": row_dtype, "batch_max": 300}
   eng = CuHNSW(engine_options(opt))
   eng.set_data(base)
   src = rng.integers(0, n, 500).astype(np.int32)
@@ -364,7 +369,7 @@ def test_half_rows_give_the_canonical_distance_over_the_rounded_values(d, dist_t
   p1, p2 = str(tmp_path / "h1.index"), str(tmp_path / "h2.index")
   eng.save_index(p1)
   assert (index_file.load(p1, dist_type).vec == base_r).all()
-  eng2 = CuHNSW(engine_options({"dist_type": dist_type, "row_dtype": "f16"}))
+  eng2 = CuHNSW(engine_options({"dist_type": dist_type, "row_dtype": row_dtype}))
   eng2.load_index(p1)
   eng2.save_index(p2)
   assert open(p1, "rb").read() == open(p2, "rb").read()
@@ -422,7 +427,7 @@ def test_half_rows_keep_recall():
     rec[dt] = ds.recall(eng.search_knn(q, 10, 200)[0], truth)
   assert rec["f16"] >= rec["f32"] - 0.01, rec
   with pytest.raises(RuntimeError, match="row_dtype"):
-    CuHNSW(engine_options(opt, row_dtype="bf16"))
+    CuHNSW(engine_options(opt, row_dtype="f8"))
 
 
 # ---------------------------------------------------------------- index file

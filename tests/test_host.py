@@ -168,8 +168,9 @@ def test_extension_options_and_their_validation():
       b.init(write_opt(tmp, {"devices": [0, -1]}))
     with pytest.raises(RuntimeError, match="disagree"):
       b.init(write_opt(tmp, {"devices": [1, 0], "device_id": 0}))
-    with pytest.raises(RuntimeError, match="row_dtype must be f32 or f16"):
-      CuHNSWBind().init(write_opt(tmp, {"row_dtype": "bf16"}))
+    assert b.init(write_opt(tmp, {"row_dtype": "bf16"}))
+    with pytest.raises(RuntimeError, match="row_dtype must be f32, f16 or bf16"):
+      CuHNSWBind().init(write_opt(tmp, {"row_dtype": "f8"}))
 
 
 def test_python_api_constructor_semantics():

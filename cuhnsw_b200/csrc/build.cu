@@ -81,11 +81,9 @@ __device__ __forceinline__ int select_neighbors(Dist& de, const unsigned long lo
       // the accepted neighbours are tested four at a time (one distance pass), closest first: most
       // candidates are turned down by one of the first ones, and the rows of the others are then never
       // read (1.18 M x 50: build 0.208 -> 0.192 s; 8 per vote 0.201 s)
-#ifndef HNSW_SEL_CHUNK
-#define HNSW_SEL_CHUNK 4
-#endif
-      for (int base = 0; base < head; base += HNSW_SEL_CHUNK) {
-        int n = min(HNSW_SEL_CHUNK, head - base);
+      constexpr int kVote = 4;
+      for (int base = 0; base < head; base += kVote) {
+        int n = min(kVote, head - base);
         int id = (lane < n) ? sel.ids[base + lane] : 0;
         float dd = de.eval(id, n);
         wc.evals += n;

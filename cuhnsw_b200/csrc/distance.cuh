@@ -121,26 +121,19 @@ template <int C, class Row = RowF32>
 struct DistSmall {
   static constexpr int kTeam = 8;
   static constexpr int kRowsPerPass = 4;
-  // Passes whose loads are issued together.  Measured on a B200: one pass per step and 64
-  // registers (32 resident warps per SM) beats deeper batches with fewer resident warps.
-#ifndef HNSW_DIST_BATCH
-#define HNSW_DIST_BATCH 1
-#endif
-  static constexpr int kBatch = HNSW_DIST_BATCH;
-  // resident CTAs (of 2 warps) per SM the walk kernels are compiled for
-  // search: 16 CTAs = 64 registers; rows of 97..128 floats spill there (56 bytes) and run 37 % faster with
-  // 14 CTAs = 72 registers (1 M x 128, 10 000 queries, ef 256: 3.52 ms against 5.57 ms)
-#ifndef HNSW_SEARCH_MIN_CTAS
-#define HNSW_SEARCH_MIN_CTAS (C <= 3 ? 16 : 14)
-#endif
+  // Passes whose loads are issued together: one.  Measured on a B200 (1.18 M x 50, 10 000 queries, ef 200):
+  // 1.50 ms per launch with one pass in flight, 1.69 ms with two, 2.04 ms with three (all at 64 registers):
+  // every added instruction costs more than the shorter gather saves.
+  static constexpr int kBatch = 1;
+  // Resident CTAs (of 2 warps) per SM the walk kernels are compiled for.
+  // search: 16 CTAs = 64 registers; 17 or 18 CTAs (56 registers, spills) gain nothing even where they save a
+  // wave of warps (1.51 ms and 2.08 ms on the same launch); rows of 97..128 floats spill at 64 registers and run
+  // 37 % faster with 14 CTAs = 72 registers (1 M x 128, 10 000 queries, ef 256: 3.52 ms against 5.57 ms)
+  static constexpr int kSearchMinCtas = C <= 3 ? 16 : 14;
   // construction: 16 CTAs (64 registers) measured 6 % faster than 12 for rows of up to 64 floats
   // (1.18 M x 50: 0.208 s against 0.222 s) and 2.5 % faster for 96 (2 M x 96: 0.310 against 0.318 s);
   // rows of 128 floats are 15 % slower there (1 M x 128: 0.477 against 0.415 s)
-#ifndef HNSW_BUILD_MIN_CTAS
-#define HNSW_BUILD_MIN_CTAS (C <= 3 ? 16 : 12)
-#endif
-  static constexpr int kSearchMinCtas = HNSW_SEARCH_MIN_CTAS;
-  static constexpr int kBuildMinCtas = HNSW_BUILD_MIN_CTAS;
+  static constexpr int kBuildMinCtas = C <= 3 ? 16 : 12;
   static constexpr int kWarpsPerSmTarget = 32;
   __host__ __device__ static constexpr size_t smem_bytes(int) { return 0; }
 

@@ -298,10 +298,7 @@ int Engine::ResolveVsize(int cap, long long nq, int* vsize) const {
     // 3576 evaluations per query and 5.67 ms with 2048 entries, 2099 and 4.98 ms with 16384.
     const int kind = nq < 0 ? kSearchWarp
                             : search_kernel_kind(d_, nq, opt_.search_team, opt_.reverse_cand ? 1 : 0, sm_count_);
-#ifndef HNSW_SEARCH_WARPS_SMALL
-#define HNSW_SEARCH_WARPS_SMALL 32
-#endif
-    const int warps = d_ <= 128 ? HNSW_SEARCH_WARPS_SMALL : kind == kSearchTeam ? 4 : kind == kSearchWarpDeep ? 8 : 16;
+    const int warps = d_ <= 128 ? 32 : kind == kSearchTeam ? 4 : kind == kSearchWarpDeep ? 8 : 16;
     const int top = kind == kSearchTeam ? 16384 : kind == kSearchWarpDeep ? 8192 : 4096;
     const long long budget = (long long)smem_optin_ / warps - 640;
     const int floor_entries = std::min(4096, std::max(512, next_pow2(4ll * cap)));

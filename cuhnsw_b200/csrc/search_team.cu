@@ -13,10 +13,7 @@
 
 namespace hnsw {
 
-#ifndef HNSW_TEAM_WARPS
-#define HNSW_TEAM_WARPS 4
-#endif
-constexpr int kTeamWarps = HNSW_TEAM_WARPS;
+constexpr int kTeamWarps = 4;
 
 struct TeamMailbox {
   int n;  // rows to evaluate; -1 = the walk is over

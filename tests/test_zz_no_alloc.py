@@ -64,3 +64,39 @@ def test_noalloc_search_rejects_requests_beyond_its_fixed_array():
   eng.obj.search_knn(fit, 10, 20, *want)
   assert (got[0] == want[0]).all() and (got[2] == want[2]).all()
   assert_same_bits(got[1], want[1])
+
+
+@pytest.mark.parametrize("d,row_dtype,nq,labelled", [(50, "f32", 300, False), (200, "f32", 40, False), (200, "f32", 2000, True),
+                                                     (96, "f16", 300, True), (50, "bf16", 300, False)])
+def test_noalloc_search_takes_no_device_memory_once_warm(d, row_dtype, nq, labelled, tmp_path):
+  """The promise is about device memory: after one warm-up call (which loads the search kernel of this row
+  width, row type and batch class, and looks the fixed array up), a call must leave the amount of free device
+  memory exactly where it was.  Covers rows wider than 128 floats (the CTA-per-query kernel for few queries, the
+  warp-per-query kernel for many), 16-bit rows and an index that came from a file (ids mapped through labels)."""
+  import torch
+  rng = np.random.default_rng(d + nq)
+  n = 6000
+  base = rng.standard_normal((n, d)).astype(np.float32)
+  q = rng.standard_normal((nq, d)).astype(np.float32)
+  opt = {"dist_type": "l2", "max_m": 12, "max_m0": 24, "ef_construction": 60, "seed": 3, "row_dtype": row_dtype,
+         "batch_max": 500}
+  eng = CuHNSW(engine_options(opt))
+  eng.set_data(base)
+  eng.build()
+  if labelled:
+    path = str(tmp_path / "n.index")
+    eng.save_index(path)
+    eng = CuHNSW(engine_options({"dist_type": "l2", "row_dtype": row_dtype}))
+    eng.load_index(path)
+  want, got = outputs(nq, 10), outputs(nq, 10)
+  eng.obj.search_knn(q, 10, 80, *want)
+  eng.obj.search_knn_noalloc(q, 10, 80, *got)  # warm-up: kernel load + address look-up
+  torch.cuda.synchronize()
+  free_before = torch.cuda.mem_get_info()[0]
+  for _ in range(3):
+    got = outputs(nq, 10)
+    eng.obj.search_knn_noalloc(q, 10, 80, *got)
+  torch.cuda.synchronize()
+  assert torch.cuda.mem_get_info()[0] == free_before, "a warmed-up call changed the free device memory"
+  assert (got[0] == want[0]).all() and (got[2] == want[2]).all()
+  assert_same_bits(got[1], want[1])

@@ -77,6 +77,8 @@ def parse():
   ap.add_argument("--ef-extra", type=int, nargs="*", default=[],
                   help="ef_search values tried after the workload's own sweep when that stops short of the recall "
                        "target (labelled as outside the sweep in the output)")
+  ap.add_argument("--ef", type=int, default=None,
+                  help="search at this ef_search whatever the recall sweep says (side measurements only)")
   ap.add_argument("--no-extra-blocks", action="store_true",
                   help="N > 1: skip the strong-scaling and sharded blocks (weak-scaling line only)")
   ap.add_argument("--no-cpu-build", action="store_true", help="skip the CPU build (no build_roofline, no cpu build time)")
@@ -292,6 +294,10 @@ def run_reference(args, rank, world):
   recalls = sweep_until_target(lambda ef: oracle.search(g, queries[:nr], topk, ef, nthreads=threads, native=native)[0],
                                truth, spec["ef_sweep"], args.ef_extra)
   ef = pick_ef(recalls)
+  if args.ef is not None:
+    ef = args.ef
+    if ef not in recalls:
+      recalls[ef] = ds.recall(oracle.search(g, queries[:nr], topk, ef, nthreads=threads, native=native)[0], truth)
   # distinct batches per step, like the GPU arm; batch 0 is the recall batch
   total = args.warmup + args.steps
   distinct = min(total, 8)
@@ -431,6 +437,10 @@ def run_ours(args, rank, world, local_rank):
 
   recalls = sweep_until_target(search_ids, truth, spec["ef_sweep"], args.ef_extra)
   ef = pick_ef(recalls)
+  if args.ef is not None:
+    ef = args.ef
+    if ef not in recalls:
+      recalls[ef] = ds.recall(search_ids(ef), truth)
 
   total = args.warmup + args.steps
   # distinct query batches per step (and per rank when the index is replicated); batch 0 of rank 0 is the

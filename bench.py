@@ -547,13 +547,20 @@ def run_ours(args, rank, world, local_rank):
   graph_for_cpu = oracle_graph_from_engine(engine, stored, spec) if (rank == 0 and not sharded) else None
   extra_blocks = {}
   if world > 1 and not sharded and not args.no_extra_blocks:
-    extra_blocks["strong"] = strong_block(args, engine, eopt, base, queries0, kept[ef], topk, ef, rank, world, dev,
-                                          flush, barrier, host_group)
+    # a failure in a side block must not cost the line its headline
+    try:
+      extra_blocks["strong"] = strong_block(args, engine, eopt, base, queries0, kept[ef], topk, ef, rank, world, dev,
+                                            flush, barrier, host_group)
+    except Exception as exc:  # pylint: disable=broad-except
+      extra_blocks["strong"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
     if args.workload == HEADLINE and args.n is None:
       del engine
-      torch.cuda.empty_cache()
-      extra_blocks["sharded"] = sharded_block(args, rank, world, dev, flush, barrier)
       engine = None
+      torch.cuda.empty_cache()
+      try:
+        extra_blocks["sharded"] = sharded_block(args, rank, world, dev, flush, barrier)
+      except Exception as exc:  # pylint: disable=broad-except
+        extra_blocks["sharded"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
 
   if rank != 0:
     if world > 1:

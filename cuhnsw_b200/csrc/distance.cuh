@@ -161,18 +161,17 @@ struct DistSmall {
 
   // Lane r (r < n <= 32, n >= 1) holds a row id; returns the distance to it in lane r.
   __device__ __forceinline__ float eval(int id, int n) {
-    return t.dist_type == DIST_DOT ? eval_t<true>(id, n) : eval_t<false>(id, n);
+    return t.dist_type == DIST_DOT ? eval_t<true, kBatch>(id, n) : eval_t<false, kBatch>(id, n);
   }
-
-  template <bool kDot>
+  template <bool kDot, int kB>
   __device__ __forceinline__ float eval_t(int id, int n) {
     const int lane = lane_id();
     const int team = lane >> 3, tl = lane & 7;
     float result = 0.0f;
-    for (int r0 = 0; r0 < n; r0 += 4 * kBatch) {
-      float4 v[kBatch][C];
+    for (int r0 = 0; r0 < n; r0 += 4 * kB) {
+      float4 v[kB][C];
 #pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
+      for (int u = 0; u < kB; ++u) {
         // rows past n are folded onto row 0 of the list: a harmless repeated load whose result nobody selects
         const int r = r0 + 4 * u + team;
         const int rid = __shfl_sync(FULL, id, r < n ? r : 0);
@@ -180,7 +179,7 @@ struct DistSmall {
         Row::template load<C, 8, true>(t.vec + (size_t)rid * t.row_bytes, tl, 0, t.nchunk, v[u]);
       }
 #pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
+      for (int u = 0; u < kB; ++u) {
         if (u == 0 || r0 + 4 * u < n) {  // warp-uniform
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll

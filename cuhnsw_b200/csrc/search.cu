@@ -7,6 +7,7 @@
 // (cpp/include/cuda_search_kernels.cuh:11-165, cpp/src/cuhnsw_build.cu:210-290),
 // which re-flatten and re-upload the graph on every call, launch once per
 // layer and keep the heap in global memory.
+#include <cub/block/block_radix_sort.cuh>
 #include <cub/device/device_radix_sort.cuh>
 
 #include "kernels.h"
@@ -15,6 +16,9 @@
 namespace hnsw {
 
 constexpr int kWarpsPerCta = 2;
+// batches of up to this many queries are ordered by one CTA (sort_schedule_kernel) instead of the four kernels
+// of a device-wide radix sort (10 000 queries on a B200: 19 us in one launch against 27 us in four)
+constexpr long long kBlockSortMax = 10240;
 
 template <class Dist, bool kReverse>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, Dist::kSearchMinCtas)
@@ -102,7 +106,10 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) entry_kernel(SearchParams p
   if (lane == 0) {
     s.entry_node[qi] = cur;
     s.entry_dist[qi] = dcur;
-    s.keys[qi] = ~f2ord(dcur);
+    // sort key: farthest entry first.  Small batches are sorted by one CTA (sort_schedule_kernel), which wants
+    // the query number in the low half of the word.
+    const unsigned key = ~f2ord(dcur);
+    s.keys[qi] = p.nq <= kBlockSortMax ? ((key & 0xffff0000u) | (unsigned)qi) : key;
     s.index[qi] = (int)qi;
     if (p.stats) {
       atomicAdd(p.stats + 0, (unsigned long long)wc.evals);
@@ -133,6 +140,28 @@ static cudaError_t launch_entry_rows(const SearchParams& p, const SearchSchedule
                     : launch_entry_t<typename E::Wide>(p, s, stream);
 }
 
+// Orders up to kBlockSortMax packed words (sort key in the upper 16 bits, query number in the lower 16) with one
+// CTA: a block-wide radix sort over the key bits, stable, so equal keys stay in query order.  Writes the query
+// numbers in sorted order.
+constexpr int kBlockSortThreads = 1024, kBlockSortItems = 10;
+__global__ void __launch_bounds__(kBlockSortThreads) sort_schedule_kernel(const unsigned* __restrict__ words, int nq,
+                                                                          int* __restrict__ order) {
+  using Sort = cub::BlockRadixSort<unsigned, kBlockSortThreads, kBlockSortItems>;
+  __shared__ typename Sort::TempStorage tmp;
+  unsigned mine[kBlockSortItems];
+#pragma unroll
+  for (int i = 0; i < kBlockSortItems; ++i) {
+    const int at = threadIdx.x * kBlockSortItems + i;
+    mine[i] = at < nq ? words[at] : 0xffffffffu;
+  }
+  Sort(tmp).Sort(mine, 16, 32);
+#pragma unroll
+  for (int i = 0; i < kBlockSortItems; ++i) {
+    const int at = threadIdx.x * kBlockSortItems + i;
+    if (at < nq) order[at] = (int)(mine[i] & 0xffffu);
+  }
+}
+
 size_t search_schedule_tmp_bytes(long long nq) {
   size_t bytes = 0;
   cub::DeviceRadixSort::SortPairs(nullptr, bytes, (const unsigned*)nullptr, (unsigned*)nullptr, (const int*)nullptr,
@@ -148,6 +177,14 @@ cudaError_t schedule_search(SearchParams& p, const SearchSchedule& s, int sm_cou
 #undef CALL
   if (e != cudaSuccess) return e;
   // the upper 16 bits of the key (sign, exponent, 7 bits of mantissa) order the queries finely enough
+  if (p.nq <= kBlockSortMax) {
+    sort_schedule_kernel<<<1, kBlockSortThreads, 0, stream>>>(s.keys, (int)p.nq, s.order);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    p.order = s.order;
+    p.entry_node = s.entry_node;
+    p.entry_dist = s.entry_dist;
+    return cudaSuccess;
+  }
   size_t bytes = s.sort_tmp_bytes;
   e = cub::DeviceRadixSort::SortPairs(s.sort_tmp, bytes, (const unsigned*)s.keys, s.keys_sorted, (const int*)s.index,
                                       s.order, (int)p.nq, 16, 32, stream);

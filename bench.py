@@ -586,7 +586,9 @@ def run_ours(args, rank, world, local_rank):
     "value_by_ef": value_by_ef,
     "e2e": {"value": e2e, "unit": "queries/s", "h2d_bytes_per_step": int(nq * d * 4),
             "d2h_bytes_per_step": int(nq * topk * 8 + nq * 4), "ms_per_step": ms_e2e / args.steps},
-    "gpu_launches": args.steps * (3 if sharded else 2),  # entry kernel + search kernel (+ merge kernel when sharded); the sort between them is CUB
+    # per step: entry kernel, the schedule's sort kernel (one CTA; batches above 10 240 queries use CUB's
+    # device-wide sort instead, which is not counted), search kernel (+ merge kernel when sharded)
+    "gpu_launches": args.steps * ((3 if nq <= 10240 else 2) + (1 if sharded else 0)),
     "build_sec_per_1M": build_s / (n / 1e6), "build_seconds": build_s, "build_graph_seconds": build_graph_s,
     "level_draw_seconds": levels_s,
     "build_timing": "wall time of set_random_levels() + build_graph() (= build()) after an untimed 20 000-row warm-up build",

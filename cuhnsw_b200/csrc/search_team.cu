@@ -134,7 +134,7 @@ cudaError_t launch_search_team(const SearchParams& p0, int sm_count, cudaStream_
   SearchParams p = p0;
   const size_t smem = search_team_smem(p.g.d, p.ef, p.vsize, p.g.n);
   p.smem_per_warp = (int)smem;
-#define CALL(R) knn_search_team_kernel<typename Pick<R>::Wide>
+#define CALL(R) knn_search_team_kernel<typename Pick<R>::Team>
   auto kern = HNSW_WITH_ROWS(p.g.rows16, CALL);
 #undef CALL
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

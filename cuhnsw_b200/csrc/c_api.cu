@@ -101,6 +101,12 @@ int cuhnsw_search_knn_device(cuhnsw_handle* h, const float* d_qdata, int64_t num
     return e.SearchGraphDevice(d_qdata, num_queries, topk, ef_search, d_nns, d_distances, d_found_cnt);
   });
 }
+int cuhnsw_search_knn_async(cuhnsw_handle* h, const float* qdata, int64_t num_queries, int32_t topk, int32_t ef_search,
+                            int32_t* nns, float* distances, int32_t* found_cnt) {
+  return guarded(h, [&](hnsw::Engine& e) {
+    return e.SearchGraphAsync(qdata, num_queries, topk, ef_search, nns, distances, found_cnt);
+  });
+}
 int cuhnsw_search_knn_noalloc(cuhnsw_handle* h, const float* qdata, int64_t num_queries, int32_t topk,
                               int32_t ef_search, int32_t* nns, float* distances, int32_t* found_cnt) {
   return guarded(h, [&](hnsw::Engine& e) {

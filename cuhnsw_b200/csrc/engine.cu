@@ -453,26 +453,50 @@ int Engine::SearchGraphDevice(const float* d_q, long long nq, int topk, int ef, 
   p.out_ids = d_nns;
   p.out_dist = d_dist;
   p.out_found = d_found;
-  p.ticket = counters_.get();
+  SearchLane* lane = nullptr;
+  if ((rc = LaneFor(stream_, &lane)) != kOk) return rc;
+  p.ticket = lane->ticket.get();
   p.stats = stats_on_ ? counters_.get() + 4 : nullptr;
   SearchSchedule sched;
   // the launcher schedules only batches of more than one wave of its kernel (4 CTAs to 32 warps per SM);
   // below the smallest wave there is nothing to prepare
   const bool schedule = nq > (long long)sm_count_ * 4 && opt_.search_schedule;
-  if (schedule && (rc = PrepareSchedule(nq, &sched)) != kOk) return rc;
+  if (schedule && (rc = PrepareSchedule(nq, lane, &sched)) != kOk) return rc;
   CU(launch_search(p, sm_count_, stream_, schedule ? &sched : nullptr));
   return kOk;
 }
 
-int Engine::PrepareSchedule(long long nq, SearchSchedule* s) {
-  if (nq > sched_capacity_) {
-    const long long cap = std::max<long long>(nq, 1024);
-    CU(sched_d_.reserve((size_t)cap * 6));
-    CU(sched_tmp_.reserve(search_schedule_tmp_bytes(cap)));
-    sched_capacity_ = cap;
+int Engine::LaneFor(cudaStream_t stream, SearchLane** out) {
+  SearchLane* pick = nullptr;
+  for (SearchLane& l : lanes_)
+    if (l.used && l.stream == stream) pick = &l;
+  if (!pick) {
+    for (SearchLane& l : lanes_)
+      if (!l.used && !pick) pick = &l;
+    if (!pick) {
+      pick = &lanes_[0];
+      for (SearchLane& l : lanes_)
+        if (l.stamp < pick->stamp) pick = &l;
+      CU(cudaStreamSynchronize(pick->stream));  // whatever it served last is over before another stream uses it
+    }
+    if (!pick->ticket.get()) CU(pick->ticket.alloc(1));
+    pick->stream = stream;
+    pick->used = true;
   }
-  unsigned* base = sched_d_.get();
-  const long long c = sched_capacity_;
+  pick->stamp = ++lane_clock_;
+  *out = pick;
+  return kOk;
+}
+
+int Engine::PrepareSchedule(long long nq, SearchLane* lane, SearchSchedule* s) {
+  if (nq > lane->capacity) {
+    const long long cap = std::max<long long>(nq, 1024);
+    CU(lane->sched.reserve((size_t)cap * 6));
+    CU(lane->sched_tmp.reserve(search_schedule_tmp_bytes(cap)));
+    lane->capacity = cap;
+  }
+  unsigned* base = lane->sched.get();
+  const long long c = lane->capacity;
   s->capacity = c;
   s->entry_node = reinterpret_cast<int*>(base);
   s->entry_dist = reinterpret_cast<float*>(base + c);
@@ -480,29 +504,37 @@ int Engine::PrepareSchedule(long long nq, SearchSchedule* s) {
   s->keys_sorted = base + 3 * c;
   s->index = reinterpret_cast<int*>(base + 4 * c);
   s->order = reinterpret_cast<int*>(base + 5 * c);
-  s->sort_tmp = sched_tmp_.get();
-  s->sort_tmp_bytes = sched_tmp_.size();
+  s->sort_tmp = lane->sched_tmp.get();
+  s->sort_tmp_bytes = lane->sched_tmp.size();
   return kOk;
 }
 
 int Engine::SearchGraph(const float* q, long long nq, int topk, int ef, int* nns, float* dist, int* found) {
+  int rc = SearchGraphAsync(q, nq, topk, ef, nns, dist, found);
+  if (rc) return rc;
+  CU(cudaStreamSynchronize(stream_));
+  return kOk;
+}
+
+int Engine::SearchGraphAsync(const float* q, long long nq, int topk, int ef, int* nns, float* dist, int* found) {
   if (!has_graph_) return Fail(kBadState, "no graph: call build_graph() or load_index() first");
   if (nq < 0 || topk < 1) return Fail(kInvalidArgument, "need num_queries >= 0 and topk >= 1");
   if (nq == 0) return kOk;
   if (!q || !nns || !dist || !found) return Fail(kInvalidArgument, "null buffer");
   int rc = EnsureDevice();
   if (rc) return rc;
-  CU(q_d_.reserve((size_t)nq * d_));
-  CU(ids_d_.reserve((size_t)nq * topk));
-  CU(dist_d_.reserve((size_t)nq * topk));
-  CU(found_d_.reserve((size_t)nq));
-  CU(cudaMemcpyAsync(q_d_.get(), q, (size_t)nq * d_ * sizeof(float), cudaMemcpyHostToDevice, stream_));
-  rc = SearchGraphDevice(q_d_.get(), nq, topk, ef, ids_d_.get(), dist_d_.get(), found_d_.get());
+  SearchLane* lane = nullptr;
+  if ((rc = LaneFor(stream_, &lane)) != kOk) return rc;
+  CU(lane->q.reserve((size_t)nq * d_));
+  CU(lane->ids.reserve((size_t)nq * topk));
+  CU(lane->dist.reserve((size_t)nq * topk));
+  CU(lane->found.reserve((size_t)nq));
+  CU(cudaMemcpyAsync(lane->q.get(), q, (size_t)nq * d_ * sizeof(float), cudaMemcpyHostToDevice, stream_));
+  rc = SearchGraphDevice(lane->q.get(), nq, topk, ef, lane->ids.get(), lane->dist.get(), lane->found.get());
   if (rc) return rc;
-  CU(cudaMemcpyAsync(nns, ids_d_.get(), (size_t)nq * topk * sizeof(int), cudaMemcpyDeviceToHost, stream_));
-  CU(cudaMemcpyAsync(dist, dist_d_.get(), (size_t)nq * topk * sizeof(float), cudaMemcpyDeviceToHost, stream_));
-  CU(cudaMemcpyAsync(found, found_d_.get(), (size_t)nq * sizeof(int), cudaMemcpyDeviceToHost, stream_));
-  CU(cudaStreamSynchronize(stream_));
+  CU(cudaMemcpyAsync(nns, lane->ids.get(), (size_t)nq * topk * sizeof(int), cudaMemcpyDeviceToHost, stream_));
+  CU(cudaMemcpyAsync(dist, lane->dist.get(), (size_t)nq * topk * sizeof(float), cudaMemcpyDeviceToHost, stream_));
+  CU(cudaMemcpyAsync(found, lane->found.get(), (size_t)nq * sizeof(int), cudaMemcpyDeviceToHost, stream_));
   return kOk;
 }
 

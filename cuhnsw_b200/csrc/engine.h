@@ -106,6 +106,10 @@ class Engine {
   // host buffers in, host buffers out; blocks until the results are in place
   int SearchGraph(const float* qdata, long long num_queries, int topk, int ef_search, int* nns, float* distances,
                   int* found_cnt);
+  // host buffers in/out, copies and kernels enqueued on the engine's stream, returns without waiting: the
+  // results are in place once the stream has reached this point
+  int SearchGraphAsync(const float* qdata, long long num_queries, int topk, int ef_search, int* nns, float* distances,
+                       int* found_cnt);
   // device buffers in/out; enqueued on the engine's stream, returns without waiting
   int SearchGraphDevice(const float* d_qdata, long long num_queries, int topk, int ef_search, int* d_nns,
                         float* d_distances, int* d_found_cnt);
@@ -162,14 +166,28 @@ class Engine {
   DevBuf<int> rows0_, rowsU_, levels_d_, upper_base_d_, labels_d_;
   DevBuf<unsigned long long> counters_;  // [0] search ticket, [1..2] build tickets, [4..7] stats
   bool stats_on_ = false;
-  // grow-only staging for the host-pointer search path
-  DevBuf<float> q_d_, dist_d_;
-  DevBuf<int> ids_d_, found_d_;
-  // grow-only scratch of the longest-first schedule: six arrays of one word per query + sort storage
-  DevBuf<unsigned> sched_d_;
-  DevBuf<unsigned char> sched_tmp_;
-  long long sched_capacity_ = 0;
-  int PrepareSchedule(long long nq, SearchSchedule* s);
+  // Scratch of one search in flight: its ticket counter and the grow-only arrays of the
+  // longest-first schedule (six words per query + sort storage).  A search uses the set that belongs to the
+  // stream it is enqueued on, so searches enqueued on different streams can run at the same time: the tail of
+  // one batch (a launch lasts as long as its longest walk) overlaps with the next batch.  A stream beyond
+  // kSearchLanes takes over the least recently used set after waiting for the stream that used it.
+  struct SearchLane {
+    cudaStream_t stream = nullptr;
+    bool used = false;
+    unsigned long long stamp = 0;
+    DevBuf<unsigned long long> ticket;
+    DevBuf<unsigned> sched;
+    DevBuf<unsigned char> sched_tmp;
+    long long capacity = 0;
+    // grow-only device copies of the host-buffer searches' queries and results
+    DevBuf<float> q, dist;
+    DevBuf<int> ids, found;
+  };
+  static constexpr int kSearchLanes = 4;
+  SearchLane lanes_[kSearchLanes];
+  unsigned long long lane_clock_ = 0;
+  int LaneFor(cudaStream_t stream, SearchLane** lane);
+  int PrepareSchedule(long long nq, SearchLane* lane, SearchSchedule* s);
   double last_build_seconds_ = 0.0;
 };
 

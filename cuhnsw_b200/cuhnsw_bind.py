@@ -32,6 +32,8 @@ SIGNATURES = {
                                        ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
   "cuhnsw_search_knn_device": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
                                               ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_search_knn_async": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
+                                             ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
   "cuhnsw_search_knn_noalloc": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
                                                ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
   "cuhnsw_batch_distance": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
@@ -160,6 +162,12 @@ class CuHNSWBind:
     """All arguments are device addresses (ints); enqueued, not waited for."""
     self._check(self._lib.cuhnsw_search_knn_device(self._h, q_ptr, nq, topk, ef_search, nns_ptr, dist_ptr,
                                                    found_ptr))
+
+  def search_knn_async(self, q_ptr, nq, topk, ef_search, nns_ptr, dist_ptr, found_ptr):
+    """search_knn without the final wait.  All arguments are HOST addresses (ints) of page-locked buffers;
+    the results are complete once the engine's stream (set_stream) has reached this point."""
+    self._check(self._lib.cuhnsw_search_knn_async(self._h, q_ptr, nq, topk, ef_search, nns_ptr, dist_ptr,
+                                                  found_ptr))
 
   def search_knn_noalloc(self, qdata, topk, ef_search, nns, distances, found):
     """search_knn for callers that cannot allocate device memory: device staging comes from a fixed

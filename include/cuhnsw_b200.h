@@ -80,6 +80,19 @@ int cuhnsw_search_knn(cuhnsw_handle* h, const float* qdata, int64_t num_queries,
 int cuhnsw_search_knn_device(cuhnsw_handle* h, const float* d_qdata, int64_t num_queries, int32_t topk,
                              int32_t ef_search, int32_t* d_nns, float* d_distances, int32_t* d_found_cnt);
 
+/* cuhnsw_search_knn without the wait at its end: the copy of the queries to the GPU, the kernels and the copies
+ * of the results back are enqueued on the engine's stream (cuhnsw_set_stream) and the call returns; nns,
+ * distances and found_cnt are complete once that stream has reached this point (cuhnsw_synchronize, or the
+ * caller's own event).  The host buffers should be page-locked, or the copies wait for the host.  No counterpart in
+ * the reference, whose SearchGraph blocks (cpp/src/cuhnsw_build.cu:210-290).
+ * Searches enqueued on DIFFERENT streams (set the stream before each call; this call and cuhnsw_search_knn_device)
+ * may run at the same time: every stream gets its own scratch, up to four streams at once, a fifth waits for
+ * the least recently used one.  A launch lasts as long as its longest walk, so a serving loop that rotates its
+ * batches over two to four streams fills the tail of each batch with the next one.  One host thread per handle,
+ * as for every other call.  A handle with `devices` set searches on its first device only through this call. */
+int cuhnsw_search_knn_async(cuhnsw_handle* h, const float* qdata, int64_t num_queries, int32_t topk, int32_t ef_search,
+                            int32_t* nns, float* distances, int32_t* found_cnt);
+
 /* Search for callers that must not allocate.  No counterpart in the reference (its SearchGraph allocates a dozen
  * device vectors per call, cpp/src/cuhnsw_build.cu:241-249).  Same arguments and results as cuhnsw_search_knn (host
  * buffers), but once the index is in place (cuhnsw_set_data or cuhnsw_load_index has run on this handle: they

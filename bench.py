@@ -651,7 +651,7 @@ def run_ours(args, rank, world, local_rank):
     dist.destroy_process_group()
 
 
-def overlapped_block(args, engine, q_dev, q_pin, nq, topk, ef, dev, lanes=3):
+def overlapped_block(args, engine, q_dev, q_pin, nq, topk, ef, dev, lanes=4):
   """The timed steps once more with consecutive batches enqueued on `lanes` streams in turn: device-resident
   through cuhnsw_search_knn_device, and from page-locked host buffers through cuhnsw_search_knn_async (copy in,
   kernels, copies out, all on the batch's stream).  Event time from before the first batch to after the last."""

@@ -519,13 +519,14 @@ __global__ void pad_rows_kernel(const float* src, long long src_stride, float* d
     dst[idx] = (c < d) ? src[r * src_stride + c] : 0.0f;
   }
 }
-__global__ void unpad_rows_kernel(const float* src, float* dst, long long n, int d, int vstride) {
+__global__ void unpad_rows_kernel(const float* src, float* dst, long long dst_stride, long long n, int d,
+                                  int vstride) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long total = n * d;
   for (; idx < total; idx += (long long)gridDim.x * blockDim.x) {
     long long r = idx / d;
     int c = (int)(idx % d);
-    dst[idx] = src[r * vstride + c];
+    dst[r * dst_stride + c] = src[r * vstride + c];
   }
 }
 // half rows: rounded to nearest even and stored in the paired-column layout of RowF16 (the rows were
@@ -550,13 +551,42 @@ __global__ void pad_rows_16_kernel(const float* src, long long src_stride, H* ds
   }
 }
 template <class H>
-__global__ void unpad_rows_16_kernel(const H* src, float* dst, long long n, int d, int vstride) {
+__global__ void unpad_rows_16_kernel(const H* src, float* dst, long long dst_stride, long long n, int d,
+                                     int vstride) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long total = n * d;
   for (; idx < total; idx += (long long)gridDim.x * blockDim.x) {
     long long r = idx / d;
     int e = (int)(idx % d);
-    dst[idx] = widen16(src[r * vstride + RowF16::position(d, e)]);
+    dst[r * dst_stride + e] = widen16(src[r * vstride + RowF16::position(d, e)]);
+  }
+}
+// The inverse of unpack_links_kernel: degree word, neighbour ids packed to the front of max_m0 slots (zeros
+// after them) and the record's own number as its 64-bit label; the vector words in between are written by the
+// unpad kernels.
+__global__ void pack_links_kernel(const int* __restrict__ rows, int stride, long long count, long long first,
+                                  int max_m0, unsigned* __restrict__ records, long long rec_words) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = count * max_m0;
+  for (; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / max_m0;
+    const int j = (int)(idx % max_m0);
+    const int* row = rows + r * stride;
+    unsigned* rec = records + r * rec_words;
+    int before = 0, deg = 0;
+    for (int k = 0; k < max_m0; ++k) {
+      const int live = row[k] >= 0 ? 1 : 0;
+      deg += live;
+      before += k < j ? live : 0;
+    }
+    if (row[j] >= 0) rec[1 + before] = (unsigned)row[j];
+    if (j >= deg) rec[1 + j] = 0u;
+    if (j == 0) {
+      rec[0] = (unsigned)deg;
+      const unsigned long long label = (unsigned long long)(first + r);
+      rec[rec_words - 2] = (unsigned)label;
+      rec[rec_words - 1] = (unsigned)(label >> 32);
+    }
   }
 }
 __global__ void unpack_links_kernel(const unsigned* __restrict__ records, long long rec_words, long long count,
@@ -620,16 +650,25 @@ cudaError_t launch_unpack_links(const unsigned* records, long long rec_words, lo
                                                                       rows, stride, labels, bad);
   return cudaGetLastError();
 }
-cudaError_t launch_unpad_rows(const void* src, float* dst, long long n, int d, int vstride, int rows16,
-                              cudaStream_t stream) {
+cudaError_t launch_unpad_rows(const void* src, float* dst, long long dst_stride, long long n, int d, int vstride,
+                              int rows16, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
   if (rows16 == kRowsBF16)
-    unpad_rows_16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), dst, n, d,
-                                                                vstride);
+    unpad_rows_16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), dst,
+                                                                dst_stride, n, d, vstride);
   else if (rows16)
-    unpad_rows_16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(static_cast<const __half*>(src), dst, n, d, vstride);
+    unpad_rows_16_kernel<<<blocks_for(n * d), 256, 0, stream>>>(static_cast<const __half*>(src), dst, dst_stride, n,
+                                                                d, vstride);
   else
-    unpad_rows_kernel<<<blocks_for(n * d), 256, 0, stream>>>(static_cast<const float*>(src), dst, n, d, vstride);
+    unpad_rows_kernel<<<blocks_for(n * d), 256, 0, stream>>>(static_cast<const float*>(src), dst, dst_stride, n, d,
+                                                             vstride);
+  return cudaGetLastError();
+}
+cudaError_t launch_pack_links(const int* rows, int stride, long long count, long long first, int max_m0,
+                              unsigned* records, long long rec_words, cudaStream_t stream) {
+  if (count <= 0) return cudaSuccess;
+  pack_links_kernel<<<blocks_for(count * max_m0), 256, 0, stream>>>(rows, stride, count, first, max_m0, records,
+                                                                    rec_words);
   return cudaGetLastError();
 }
 cudaError_t launch_fill_i32(int* p, long long n, int v, cudaStream_t stream) {

@@ -688,63 +688,64 @@ int Engine::SaveIndex(const char* path) {
   h.mult = opt_.level_mult;
   h.ef_construction = (uint64_t)opt_.ef_construction;
   bool ok = std::fwrite(&h, sizeof(h), 1, f) == 1;
-  // level-0 records, in chunks of rows
+  // Level-0 records are put together on the device, 32 MB at a time, exactly as they lie in the file: one
+  // kernel packs the adjacency rows into degree word + neighbour slots and writes the labels, another moves
+  // the vectors out of their padded (fp32 or 16-bit) rows; the host only writes the chunk out.  Labels of a
+  // loaded index are 64-bit values the device does not hold: the host patches those in.
+  const long long rec_words = (long long)(rec / 4);
   const long long chunk = std::max<long long>(1, (32ll << 20) / (long long)rec);
-  std::vector<int> rows((size_t)std::min(chunk, std::max<long long>(n_, 1)) * stride0_);
-  std::vector<float> vecs((size_t)std::min(chunk, std::max<long long>(n_, 1)) * d_);
-  DevBuf<float> unpadded;  // the file holds fp32 rows without padding, whatever the storage type
-  CU(unpadded.alloc(vecs.size()));
-  std::vector<unsigned char> out((size_t)std::min(chunk, std::max<long long>(n_, 1)) * rec);
+  const size_t chunk_rows = (size_t)std::min(chunk, std::max<long long>(n_, 1));
+  DevBuf<unsigned> packed;
+  CU(packed.alloc(chunk_rows * (size_t)rec_words));
+  std::vector<unsigned char> out(chunk_rows * rec);
   for (long long s = 0; s < n_ && ok; s += chunk) {
     const long long r = std::min(chunk, n_ - s);
-    CU(cudaMemcpy(rows.data(), rows0_.get() + (size_t)s * stride0_, (size_t)r * stride0_ * sizeof(int),
-                  cudaMemcpyDeviceToHost));
-    CU(launch_unpad_rows(RowPtr(s), unpadded.get(), r, d_, vstride_, rows16_, stream_));
-    CU(cudaMemcpyAsync(vecs.data(), unpadded.get(), (size_t)r * d_ * sizeof(float), cudaMemcpyDeviceToHost, stream_));
+    CU(launch_pack_links(rows0_.get() + (size_t)s * stride0_, stride0_, r, s, m0, packed.get(), rec_words, stream_));
+    CU(launch_unpad_rows(RowPtr(s), reinterpret_cast<float*>(packed.get()) + 1 + m0, rec_words, r, d_, vstride_,
+                         rows16_, stream_));
+    CU(cudaMemcpyAsync(out.data(), packed.get(), (size_t)r * rec, cudaMemcpyDeviceToHost, stream_));
     CU(cudaStreamSynchronize(stream_));
-    std::memset(out.data(), 0, (size_t)r * rec);
-    for (long long i = 0; i < r; ++i) {
-      unsigned char* o = out.data() + (size_t)i * rec;
-      const int* row = rows.data() + (size_t)i * stride0_;
-      uint32_t deg = 0;
-      for (int j = 0; j < m0; ++j)
-        if (row[j] >= 0) {
-          uint32_t id = (uint32_t)row[j];
-          std::memcpy(o + 4 + 4 * (size_t)deg, &id, 4);
-          ++deg;
-        }
-      std::memcpy(o, &deg, 4);
-      std::memcpy(o + 4 + 4 * (size_t)m0, vecs.data() + (size_t)i * d_, 4 * (size_t)d_);
-      uint64_t label = labelled_ ? (uint64_t)labels_h_[(size_t)(s + i)] : (uint64_t)(s + i);
-      std::memcpy(o + rec - 8, &label, 8);
-    }
+    if (labelled_)
+      for (long long i = 0; i < r; ++i) {
+        const uint64_t label = (uint64_t)labels_h_[(size_t)(s + i)];
+        std::memcpy(out.data() + (size_t)(i + 1) * rec - 8, &label, 8);
+      }
     ok = std::fwrite(out.data(), rec, (size_t)r, f) == (size_t)r;
   }
-  // upper-layer link lists
+  // upper-layer link lists: a length word per node, then its rows; gathered into the same buffer and written
+  // whenever it fills
   std::vector<int> upper((size_t)std::max<long long>(total_upper_, 1) * strideU_);
   if (total_upper_ > 0)
     CU(cudaMemcpy(upper.data(), rowsU_.get(), (size_t)total_upper_ * strideU_ * sizeof(int), cudaMemcpyDeviceToHost));
   const size_t per_link = 4 + 4 * (size_t)m;
-  std::vector<unsigned char> lbuf;
+  size_t fill = 0;
+  auto flush = [&]() {
+    if (fill && ok) ok = std::fwrite(out.data(), 1, fill, f) == fill;
+    fill = 0;
+  };
+  out.resize(std::max<size_t>(out.size(), 4 + per_link * (size_t)(max_level_ + 1)));
   for (long long i = 0; i < n_ && ok; ++i) {
     const int lv = levels_h_[(size_t)i];
-    uint32_t nbytes = (uint32_t)(per_link * (size_t)lv);
-    lbuf.assign(4 + (size_t)nbytes, 0);
-    std::memcpy(lbuf.data(), &nbytes, 4);
+    const uint32_t nbytes = (uint32_t)(per_link * (size_t)lv);
+    if (fill + 4 + nbytes > out.size()) flush();
+    unsigned char* o = out.data() + fill;
+    std::memcpy(o, &nbytes, 4);
+    std::memset(o + 4, 0, nbytes);
     for (int l = 0; l < lv; ++l) {
       const int* row = upper.data() + ((size_t)upper_base_h_[(size_t)i] + l) * strideU_;
-      unsigned char* o = lbuf.data() + 4 + per_link * (size_t)l;
+      unsigned char* ol = o + 4 + per_link * (size_t)l;
       uint32_t deg = 0;
       for (int j = 0; j < m; ++j)
         if (row[j] >= 0) {
-          uint32_t id = (uint32_t)row[j];
-          std::memcpy(o + 4 + 4 * (size_t)deg, &id, 4);
+          const uint32_t id = (uint32_t)row[j];
+          std::memcpy(ol + 4 + 4 * (size_t)deg, &id, 4);
           ++deg;
         }
-      std::memcpy(o, &deg, 4);
+      std::memcpy(ol, &deg, 4);
     }
-    ok = std::fwrite(lbuf.data(), 1, lbuf.size(), f) == lbuf.size();
+    fill += 4 + nbytes;
   }
+  flush();
   guard.f = nullptr;
   ok = (std::fclose(f) == 0) && ok;
   if (!ok) return Fail(kIoError, std::string("short write to ") + path);

@@ -183,7 +183,7 @@ class Engine {
     DevBuf<float> q, dist;
     DevBuf<int> ids, found;
   };
-  static constexpr int kSearchLanes = 4;
+  static constexpr int kSearchLanes = 8;
   SearchLane lanes_[kSearchLanes];
   unsigned long long lane_clock_ = 0;
   int LaneFor(cudaStream_t stream, SearchLane** lane);

@@ -131,8 +131,8 @@ int row_stride_elements(int d, int rows16);
 // halves, and back
 cudaError_t launch_pad_rows(const float* src, long long src_stride, void* dst, long long n, int d, int vstride,
                             int rows16, cudaStream_t stream);
-cudaError_t launch_unpad_rows(const void* src, float* dst, long long n, int d, int vstride, int rows16,
-                              cudaStream_t stream);
+cudaError_t launch_unpad_rows(const void* src, float* dst, long long dst_stride, long long n, int d, int vstride,
+                              int rows16, cudaStream_t stream);
 cudaError_t launch_fill_i32(int* p, long long n, int v, cudaStream_t stream);
 // Level-0 records of an hnswlib index file, already on the device (`count` records of `rec_words` 32-bit words:
 // degree word, max_m0 neighbour slots, the vector, a 64-bit label): writes the -1 padded adjacency rows and
@@ -142,6 +142,12 @@ cudaError_t launch_fill_i32(int* p, long long n, int v, cudaStream_t stream);
 cudaError_t launch_unpack_links(const unsigned* records, long long rec_words, long long count, long long first,
                                 int max_m0, long long n, int* rows, int stride, int* labels,
                                 unsigned long long* bad, cudaStream_t stream);
+// The other direction, for save_index: `count` adjacency rows become the degree word, the packed neighbour
+// slots and the label (= first + record number) of level-0 records laid out on the device as in the file
+// (cpp/src/cuhnsw_base.cu:196-214); launch_unpad_rows with dst = records + 1 + max_m0 and dst_stride = rec_words
+// fills in the vectors.
+cudaError_t launch_pack_links(const int* rows, int stride, long long count, long long first, int max_m0,
+                              unsigned* records, long long rec_words, cudaStream_t stream);
 // merges per-shard rows (part p at ids/dist + p * part_stride, nq x k each, -1 = empty; offsets[p], when given,
 // turns shard-local ids into global ones) into nq x k rows ordered by (distance, id)
 cudaError_t launch_merge_topk(const int* ids, const float* dist, long long part_stride, const int* offsets, int parts,

@@ -86,7 +86,7 @@ int cuhnsw_search_knn_device(cuhnsw_handle* h, const float* d_qdata, int64_t num
  * caller's own event).  The host buffers should be page-locked, or the copies wait for the host.  No counterpart in
  * the reference, whose SearchGraph blocks (cpp/src/cuhnsw_build.cu:210-290).
  * Searches enqueued on DIFFERENT streams (set the stream before each call; this call and cuhnsw_search_knn_device)
- * may run at the same time: every stream gets its own scratch, up to four streams at once, a fifth waits for
+ * may run at the same time: every stream gets its own scratch, up to eight streams at once, a ninth waits for
  * the least recently used one.  A launch lasts as long as its longest walk, so a serving loop that rotates its
  * batches over two to four streams fills the tail of each batch with the next one.  One host thread per handle,
  * as for every other call.  A handle with `devices` set searches on its first device only through this call. */

@@ -19,13 +19,13 @@ def _engine(n, nq):
   return eng, q
 
 
-@pytest.mark.parametrize("streams", [2, 3, 6])
+@pytest.mark.parametrize("streams", [2, 3, 10])
 def test_device_searches_on_several_streams_give_the_blocking_answers(streams):
-  """7000 queries per batch: more than one wave, so every batch also uses its stream's schedule arrays.  Six
-  streams are more than the engine keeps scratch for: the fifth and sixth take over a set after a wait."""
+  """7000 queries per batch: more than one wave, so every batch also uses its stream's schedule arrays.  Ten
+  streams are more than the engine keeps scratch for: the ninth and tenth take over a set after a wait."""
   import torch
   eng, q = _engine(30000, 7000)
-  batches = [np.ascontiguousarray(np.roll(q, 911 * b, axis=0)) for b in range(8)]
+  batches = [np.ascontiguousarray(np.roll(q, 911 * b, axis=0)) for b in range(12)]
   want = [eng.search_knn(b, 10, 48) for b in batches]
   pool = [torch.cuda.Stream() for _ in range(streams)]
   dq = [torch.from_numpy(b).cuda() for b in batches]

@@ -46,7 +46,14 @@ static_assert(sizeof(FileHeader) == 96, "hnswlib header is 96 bytes");
 }  // namespace
 
 Engine::Engine() {}
-Engine::~Engine() {}
+Engine::~Engine() {
+  for (SearchLane& l : lanes_)
+    if (l.done) {
+      if (device_ >= 0) cudaSetDevice(device_);
+      cudaEventSynchronize(l.done);
+      cudaEventDestroy(l.done);
+    }
+}
 
 int Engine::Fail(int code, const std::string& msg) {
   err_ = msg;
@@ -205,6 +212,8 @@ int Engine::SetData(const float* data, long long num_data, int num_dims) {
 int Engine::AllocRows(long long num_data, int num_dims) {
   int rc = EnsureDevice();
   if (rc) return rc;
+  // searches still running on other streams read the rows and the graph that are replaced from here on
+  if ((rc = WaitForSearches()) != kOk) return rc;
   n_ = num_data;
   d_ = num_dims;
   rows16_ = opt_.row_dtype == "f16" ? 1 : opt_.row_dtype == "bf16" ? 2 : 0;
@@ -315,6 +324,7 @@ int Engine::BuildGraph() {
   if (!has_levels_) return Fail(kBadState, "set_random_levels() must be called before build_graph()");
   int rc = EnsureDevice();
   if (rc) return rc;
+  if ((rc = WaitForSearches()) != kOk) return rc;
   auto t0 = std::chrono::steady_clock::now();
   if (n_ == 0) {
     has_graph_ = true;
@@ -463,7 +473,7 @@ int Engine::SearchGraphDevice(const float* d_q, long long nq, int topk, int ef, 
   const bool schedule = nq > (long long)sm_count_ * 4 && opt_.search_schedule;
   if (schedule && (rc = PrepareSchedule(nq, lane, &sched)) != kOk) return rc;
   CU(launch_search(p, sm_count_, stream_, schedule ? &sched : nullptr));
-  return kOk;
+  return MarkLane(lane);
 }
 
 int Engine::LaneFor(cudaStream_t stream, SearchLane** out) {
@@ -477,14 +487,31 @@ int Engine::LaneFor(cudaStream_t stream, SearchLane** out) {
       pick = &lanes_[0];
       for (SearchLane& l : lanes_)
         if (l.stamp < pick->stamp) pick = &l;
-      CU(cudaStreamSynchronize(pick->stream));  // whatever it served last is over before another stream uses it
+      if (pick->pending) CU(cudaEventSynchronize(pick->done));  // its last search is over before another stream uses it
+      pick->pending = false;
     }
     if (!pick->ticket.get()) CU(pick->ticket.alloc(1));
+    if (!pick->done) CU(cudaEventCreateWithFlags(&pick->done, cudaEventDisableTiming));
     pick->stream = stream;
     pick->used = true;
   }
   pick->stamp = ++lane_clock_;
   *out = pick;
+  return kOk;
+}
+
+int Engine::MarkLane(SearchLane* lane) {
+  CU(cudaEventRecord(lane->done, stream_));
+  lane->pending = true;
+  return kOk;
+}
+
+int Engine::WaitForSearches() {
+  for (SearchLane& l : lanes_)
+    if (l.pending) {
+      CU(cudaEventSynchronize(l.done));
+      l.pending = false;
+    }
   return kOk;
 }
 
@@ -535,7 +562,7 @@ int Engine::SearchGraphAsync(const float* q, long long nq, int topk, int ef, int
   CU(cudaMemcpyAsync(nns, lane->ids.get(), (size_t)nq * topk * sizeof(int), cudaMemcpyDeviceToHost, stream_));
   CU(cudaMemcpyAsync(dist, lane->dist.get(), (size_t)nq * topk * sizeof(float), cudaMemcpyDeviceToHost, stream_));
   CU(cudaMemcpyAsync(found, lane->found.get(), (size_t)nq * sizeof(int), cudaMemcpyDeviceToHost, stream_));
-  return kOk;
+  return MarkLane(lane);  // the staging buffers are in use until the copies are through
 }
 
 int Engine::SearchGraphStatic(const float* q, long long nq, int topk, int ef, int* nns, float* dist, int* found) {

@@ -170,11 +170,14 @@ class Engine {
   // longest-first schedule (six words per query + sort storage).  A search uses the set that belongs to the
   // stream it is enqueued on, so searches enqueued on different streams can run at the same time: the tail of
   // one batch (a launch lasts as long as its longest walk) overlaps with the next batch.  A stream beyond
-  // kSearchLanes takes over the least recently used set after waiting for the stream that used it.
+  // kSearchLanes takes over the least recently used set after waiting for the search that used it last (through
+  // the set's own event, which outlives a stream the caller has destroyed since).
   struct SearchLane {
     cudaStream_t stream = nullptr;
     bool used = false;
     unsigned long long stamp = 0;
+    cudaEvent_t done = nullptr;  // recorded behind the last thing a search put on the stream
+    bool pending = false;
     DevBuf<unsigned long long> ticket;
     DevBuf<unsigned> sched;
     DevBuf<unsigned char> sched_tmp;
@@ -187,6 +190,8 @@ class Engine {
   SearchLane lanes_[kSearchLanes];
   unsigned long long lane_clock_ = 0;
   int LaneFor(cudaStream_t stream, SearchLane** lane);
+  int MarkLane(SearchLane* lane);  // records `done` on the engine's stream
+  int WaitForSearches();           // every search enqueued so far, on whatever stream, is over
   int PrepareSchedule(long long nq, SearchLane* lane, SearchSchedule* s);
   double last_build_seconds_ = 0.0;
 };

@@ -89,7 +89,8 @@ int cuhnsw_search_knn_device(cuhnsw_handle* h, const float* d_qdata, int64_t num
  * may run at the same time: every stream gets its own scratch, up to eight streams at once, a ninth waits for
  * the least recently used one.  A launch lasts as long as its longest walk, so a serving loop that rotates its
  * batches over two to four streams fills the tail of each batch with the next one.  One host thread per handle,
- * as for every other call.  A handle with `devices` set searches on its first device only through this call. */
+ * as for every other call.  cuhnsw_set_data, cuhnsw_build_graph and cuhnsw_load_index first wait for every search
+ * enqueued so far; the caller may destroy a stream once its own work on it is complete.  A handle with `devices` set searches on its first device only through this call. */
 int cuhnsw_search_knn_async(cuhnsw_handle* h, const float* qdata, int64_t num_queries, int32_t topk, int32_t ef_search,
                             int32_t* nns, float* distances, int32_t* found_cnt);
 

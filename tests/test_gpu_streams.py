@@ -73,3 +73,33 @@ def test_host_buffer_searches_without_the_wait_give_the_blocking_answers():
   again = eng.search_knn(batches[0], 7, 40)
   eng.obj.set_stream(0)
   assert (again[0] == want[0][0]).all()
+
+
+def test_a_rebuild_waits_for_searches_in_flight_and_a_destroyed_stream_does_no_harm():
+  """set_data / build / load_index replace what running searches read, so they first wait for every search
+  enqueued so far, whatever its stream; a scratch set whose stream the caller has destroyed is reused through
+  the set's own event, not through the stream."""
+  import torch
+  eng, q = _engine(20000, 7000)
+  want = eng.search_knn(q, 10, 64)
+  dq = torch.from_numpy(q).cuda()
+  out = (torch.empty((len(q), 10), dtype=torch.int32, device="cuda"), torch.empty((len(q), 10), device="cuda"),
+         torch.empty(len(q), dtype=torch.int32, device="cuda"))
+  for turn in range(12):  # more short-lived streams than the engine has scratch sets
+    side = torch.cuda.Stream()
+    eng.obj.set_stream(side.cuda_stream)
+    eng.obj.search_knn_device(dq.data_ptr(), len(q), 10, 64, out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr())
+    side.synchronize()
+    assert (out[0].cpu().numpy() == want[0]).all(), turn
+    eng.obj.set_stream(0)
+    del side
+  side = torch.cuda.Stream()
+  eng.obj.set_stream(side.cuda_stream)
+  eng.obj.search_knn_device(dq.data_ptr(), len(q), 10, 64, out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr())
+  eng.obj.set_stream(0)
+  base, _, _ = small_workload("angular_toy", 5000, 16)
+  eng.set_data(base)  # must not pull the rows from under the search above
+  eng.build()
+  torch.cuda.synchronize()
+  assert (out[0].cpu().numpy() == want[0]).all()
+  assert int(eng.search_knn(q[:100], 10, 64)[0].max()) < 5000

@@ -71,6 +71,7 @@ EXTENSIONS = {
   "device_id": (int, -1),
   "search_team": (int, -1),
   "search_schedule": (bool, True),
+  "zero_copy": (bool, True),
   "row_dtype": (str, "f32"),
   # GPUs that hold a replica of the index and share every host-buffer search; empty = one GPU (device_id)
   "devices": (list, ()),

@@ -135,6 +135,7 @@ int Engine::Init(const char* opt_path, int device_override) {
   o.reverse_cand = js.boolean("reverse_cand", o.reverse_cand);
   o.search_team = (int)js.number("search_team", o.search_team);
   o.search_schedule = js.boolean("search_schedule", o.search_schedule);
+  o.zero_copy = js.boolean("zero_copy", o.zero_copy);
   o.row_dtype = js.string("row_dtype", o.row_dtype);
   if (o.row_dtype != "f32" && o.row_dtype != "f16" && o.row_dtype != "bf16")
     return Fail(kInvalidArgument, "row_dtype must be f32, f16 or bf16");
@@ -550,6 +551,24 @@ int Engine::SearchGraphAsync(const float* q, long long nq, int topk, int ef, int
   if (!q || !nns || !dist || !found) return Fail(kInvalidArgument, "null buffer");
   int rc = EnsureDevice();
   if (rc) return rc;
+  // Page-locked host buffers have a device address: the kernels then read the queries and write the results
+  // in place, over PCIe while they run, instead of a copy in before the first kernel and three copies out after
+  // the last.  Every query is read once or twice and every result word written once, so nothing is lost.
+  if (opt_.zero_copy) {
+    auto mapped = [](const void* host, void** dev) {
+      cudaPointerAttributes a;
+      if (cudaPointerGetAttributes(&a, host) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+      }
+      *dev = a.devicePointer;
+      return a.type == cudaMemoryTypeHost && a.devicePointer != nullptr;
+    };
+    void *dq = nullptr, *dn = nullptr, *dd = nullptr, *df = nullptr;
+    if (mapped(q, &dq) && mapped(nns, &dn) && mapped(dist, &dd) && mapped(found, &df))
+      return SearchGraphDevice(static_cast<const float*>(dq), nq, topk, ef, static_cast<int*>(dn),
+                               static_cast<float*>(dd), static_cast<int*>(df));
+  }
   SearchLane* lane = nullptr;
   if ((rc = LaneFor(stream_, &lane)) != kOk) return rc;
   CU(lane->q.reserve((size_t)nq * d_));

@@ -43,6 +43,7 @@ struct Options {
   int search_team = -1;  // d > 128: 1 = CTA per query, 0 = warp per query, -1 = chosen by batch size
   std::string row_dtype = "f32";  // "f16" / "bf16": rows stored in 16 bits, distances in fp32 over the stored values
   bool search_schedule = true;  // batches of more than one wave: serve the queries with the farthest entry first
+  bool zero_copy = true;        // host-buffer searches on page-locked buffers: the kernels read and write them in place
   double heuristic_coef = 0.25;
   // extensions (absent from the reference's schema; optional keys of the option file)
   long long batch_max = 0;  // nodes per insertion batch; 0 = hyper_threads * (SMs * 128 / block_dim)

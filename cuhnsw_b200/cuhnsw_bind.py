@@ -85,6 +85,7 @@ class CuHNSWBind:
     self._h = self._lib.cuhnsw_create()
     if not self._h:
       raise RuntimeError("cuhnsw_create failed")
+    self._num_dims = None  # row width of the index in place, asked for once per set_data / load_index
 
   def __del__(self):
     h, self._h = getattr(self, "_h", None), None
@@ -112,6 +113,7 @@ class CuHNSWBind:
     arr = np.ascontiguousarray(data, dtype=np.float32)
     if arr.ndim != 2:
       raise RuntimeError("data must be 2d array")
+    self._num_dims = None
     self._check(self._lib.cuhnsw_set_data(self._h, arr.ctypes.data, arr.shape[0], arr.shape[1]))
 
   def set_random_levels(self, levels):
@@ -131,6 +133,7 @@ class CuHNSWBind:
   def load_index(self, fpath):
     if isinstance(fpath, str):
       fpath = fpath.encode("utf8")
+    self._num_dims = None
     self._check(self._lib.cuhnsw_load_index(self._h, fpath))
 
   def _search_args(self, qdata, topk, nns, distances, found):
@@ -142,7 +145,9 @@ class CuHNSWBind:
     nq = 1 if q.ndim == 1 else q.shape[0]
     if int(topk) < 1:
       raise RuntimeError("topk must be at least 1")
-    num_dims = self.describe()["num_dims"]
+    if self._num_dims is None:  # fixed until the next set_data / load_index
+      self._num_dims = self.describe()["num_dims"]
+    num_dims = self._num_dims
     if num_dims > 0 and q.shape[-1] != num_dims:
       raise RuntimeError(f"queries have {q.shape[-1]} dimensions, the index has {num_dims}")
     for name, arr, dt in (("nns", nns, np.int32), ("distances", distances, np.float32), ("found", found, np.int32)):

@@ -48,7 +48,8 @@ const char* cuhnsw_last_error(const cuhnsw_handle* h);
  * devices (array of GPU numbers: the index is built or loaded on the first and copied to the others, and
  * cuhnsw_search_knn cuts every batch into contiguous slices, one per listed GPU, searched at the same time by one
  * host thread each; results equal the single-GPU results row for row; a GPU may be listed more than once),
- * batch_max, ramp_div (insertion batch schedule), search_team, search_schedule, row_dtype ("f32", "f16", "bf16"). */
+ * batch_max, ramp_div (insertion batch schedule), search_team, search_schedule, zero_copy (page-locked host
+ * buffers are read and written in place by the search kernels), row_dtype ("f32", "f16", "bf16"). */
 int cuhnsw_init(cuhnsw_handle* h, const char* opt_path);
 
 /* CuHNSWBind::SetData -> CuHNSW::SetData  (cuhnsw/bindings.cc:26-33, cpp/src/cuhnsw_base.cu:108-128).

@@ -11,9 +11,9 @@ from cuhnsw_b200 import CuHNSW
 pytestmark = pytest.mark.gpu
 
 
-def _engine(n, nq):
+def _engine(n, nq, **extra):
   base, q, opt = small_workload("angular_toy", n, nq)
-  eng = CuHNSW(engine_options(opt))
+  eng = CuHNSW(engine_options(opt, **extra))
   eng.set_data(base)
   eng.build()
   return eng, q
@@ -45,11 +45,14 @@ def test_device_searches_on_several_streams_give_the_blocking_answers(streams):
     assert_same_bits(out[b][1].cpu().numpy(), want[b][1])
 
 
-def test_host_buffer_searches_without_the_wait_give_the_blocking_answers():
-  """cuhnsw_search_knn_async with page-locked buffers on two streams, batches of different sizes (the staging
-  buffers of a stream grow between calls)."""
+@pytest.mark.parametrize("zero_copy", [True, False])
+def test_host_buffer_searches_without_the_wait_give_the_blocking_answers(zero_copy):
+  """cuhnsw_search_knn_async with page-locked buffers on two streams, batches of different sizes.  With
+  zero_copy (the default) the kernels read and write the page-locked buffers in place; without it they go
+  through the stream's staging buffers, which grow between calls.  The expected answers come from pageable
+  numpy arrays, which always take the staged path."""
   import torch
-  eng, q = _engine(20000, 6000)
+  eng, q = _engine(20000, 6000, zero_copy=zero_copy)
   sizes = [6000, 1, 2500, 6000, 37, 5999]
   batches = [np.ascontiguousarray(np.roll(q, 517 * i, axis=0)[:m]) for i, m in enumerate(sizes)]
   want = [eng.search_knn(b, 7, 40) for b in batches]

@@ -152,6 +152,31 @@ struct WarpList {
           dup = eq != 0;
         }
       }
+    } else if (__popc(km0) <= 4) {
+      // the same for lists of more than 1024 keys: a lane stands for a span of `cs` chunks, the span that holds
+      // the newcomer's place is then searched chunk by chunk
+      const int cs = (nch + 31) >> 5;
+      for (unsigned mm = km0; mm; mm &= mm - 1) {
+        const int b = __ffs(mm) - 1;
+        const unsigned long long kb = shfl64(key, b);
+        const unsigned long long pv =
+            (lane * cs < nch) ? (keys[min((lane + 1) * cs * 32 - 1, size - 1)] & KEY_MASK) : KEY_MAX;
+        const int c = __popc(__ballot_sync(FULL, pv < kb));  // spans entirely below kb
+        int below = 0;
+        bool same = false;
+        for (int j = 0; j < cs; ++j) {
+          const int i = (c * cs + j) * 32 + lane;
+          const unsigned long long kv = (i < size) ? (keys[i] & KEY_MASK) : KEY_MAX;
+          const unsigned lt = __ballot_sync(FULL, kv < kb);
+          same = same || __ballot_sync(FULL, kv == kb) != 0;
+          below += __popc(lt);
+          if (lt != 0xffffffffu) break;  // the place is in this chunk
+        }
+        if (lane == b) {
+          pos = min(c * cs * 32 + below, size);
+          dup = same;
+        }
+      }
     } else {
       int lo = 0, hi = keep ? size : 0;
       while (__any_sync(FULL, lo < hi)) {

@@ -90,7 +90,8 @@ def test_wide_rows_every_search_kernel_gives_the_oracle_answer(d, dist_type, tmp
   opt = {"dist_type": dist_type, "max_m": 12, "max_m0": 24, "ef_construction": 100, "level_mult": 0.4, "seed": 5}
   levels = ds.random_levels(n, opt["seed"], opt["level_mult"])
   g = oracle.build_graph(base, levels, 12, 24, dist_type, 100, bmax=512)
-  want = {ef: oracle.search(g, q, 10, ef) for ef in (10, 100, 400)}
+  # ef 1500: lists long enough for the CTA-per-query kernel to move their keys with all four warps
+  want = {ef: oracle.search(g, q, 10, ef) for ef in (10, 100, 400, 1500)}
   for team in (1, 0, -1):
     eng = engine_from_oracle_graph(g, opt, tmp_path, search_team=team)
     for ef, (oids, odist, ofound) in want.items():

@@ -84,15 +84,18 @@ def test_list_merge_small_cases(name):
   assert run_list(cap, batches, expand) == model_list(cap, batches, expand)
 
 
-@pytest.mark.parametrize("cap,seed", [(10, 1), (33, 2), (64, 3), (200, 4), (300, 5), (1000, 6)])
-def test_list_merge_random_walks(cap, seed):
-  """Batches of 0 to 32 keys drawn from a small set of distances (so that ties and re-offers are common),
-  with expansions in between, as a walk produces them."""
+@pytest.mark.parametrize("cap,seed,rounds,most", [(10, 1, 120, 32), (33, 2, 120, 32), (64, 3, 120, 32),
+                                                  (200, 4, 120, 32), (300, 5, 120, 32), (1000, 6, 120, 32),
+                                                  (3000, 7, 900, 6), (8192, 8, 700, 20)])
+def test_list_merge_random_walks(cap, seed, rounds, most):
+  """Batches of 0 to `most` keys drawn from a small set of distances (so that ties and re-offers are common),
+  with expansions in between, as a walk produces them.  The last two cases grow lists of more than 1024 keys,
+  whose insertion places are searched span by span."""
   rng = np.random.default_rng(seed)
-  pool_d = rng.standard_normal(40).astype(np.float32)
+  pool_d = rng.standard_normal(40 if cap <= 1000 else 400).astype(np.float32)
   batches, expand, offered = [], [], []
-  for _ in range(120):
-    n = int(rng.integers(0, 33))
+  for _ in range(rounds):
+    n = int(rng.integers(0, most + 1))
     batch = {}
     while len(batch) < n:
       if offered and rng.random() < 0.2:

@@ -122,6 +122,29 @@ int cuhnsw_set_stream(cuhnsw_handle* h, void* cuda_stream) {
 int cuhnsw_synchronize(cuhnsw_handle* h) {
   return guarded(h, [&](hnsw::Engine& e) { return e.Synchronize(); });
 }
+int cuhnsw_stream_create(cuhnsw_handle* h, void** out_stream) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.CreateStream(out_stream); });
+}
+int cuhnsw_stream_synchronize(cuhnsw_handle* h, void* cuda_stream) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.SyncStream(cuda_stream); });
+}
+int cuhnsw_stream_destroy(cuhnsw_handle* h, void* cuda_stream) {
+  return guarded(h, [&](hnsw::Engine& e) { return e.DestroyStream(cuda_stream); });
+}
+void* cuhnsw_host_alloc(cuhnsw_handle* h, size_t bytes) {
+  void* p = nullptr;
+  guarded(h, [&](hnsw::Engine& e) {
+    p = e.HostAlloc(bytes);
+    return hnsw::kOk;
+  });
+  return p;
+}
+void cuhnsw_host_free(cuhnsw_handle* h, void* ptr) {
+  guarded(h, [&](hnsw::Engine& e) {
+    e.HostFree(ptr);
+    return hnsw::kOk;
+  });
+}
 int cuhnsw_enable_stats(cuhnsw_handle* h, int32_t on) {
   return guarded(h, [&](hnsw::Engine& e) { return e.EnableStats(on); });
 }

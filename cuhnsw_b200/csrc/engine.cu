@@ -179,6 +179,45 @@ int Engine::SetStream(void* stream) {
   return kOk;
 }
 
+int Engine::CreateStream(void** out) {
+  if (!out) return Fail(kInvalidArgument, "null out_stream");
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  cudaStream_t s = nullptr;
+  CU(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  *out = s;
+  return kOk;
+}
+
+int Engine::SyncStream(void* stream) {
+  int rc = EnsureDevice();
+  if (rc) return rc;
+  CU(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
+  return kOk;
+}
+
+int Engine::DestroyStream(void* stream) {
+  int rc = SyncStream(stream);
+  if (rc) return rc;
+  if (stream_ == reinterpret_cast<cudaStream_t>(stream)) stream_ = nullptr;  // back to the default stream
+  if (stream) CU(cudaStreamDestroy(reinterpret_cast<cudaStream_t>(stream)));
+  return kOk;
+}
+
+void* Engine::HostAlloc(size_t bytes) {
+  if (EnsureDevice() != kOk) return nullptr;
+  void* p = nullptr;
+  if (cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocPortable) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return p;
+}
+
+void Engine::HostFree(void* ptr) {
+  if (ptr && EnsureDevice() == kOk) cudaFreeHost(ptr);
+}
+
 int Engine::Synchronize() {
   int rc = EnsureDevice();
   if (rc) return rc;

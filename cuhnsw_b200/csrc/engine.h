@@ -121,6 +121,12 @@ class Engine {
   int BatchDistance(const int* src, const int* dst, long long npairs, float* out);
   int SetStream(void* stream);
   int Synchronize();
+  // a stream on this engine's GPU / page-locked host memory, for hosts that have no CUDA binding of their own
+  int CreateStream(void** out);
+  int SyncStream(void* stream);
+  int DestroyStream(void* stream);
+  void* HostAlloc(size_t bytes);
+  void HostFree(void* ptr);
   int EnableStats(int on);
   int GetStats(unsigned long long* out4);
   int GetGraph(int* levels, int* rows0, int* rows_upper);  // host copies, for tests

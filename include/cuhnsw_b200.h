@@ -129,6 +129,16 @@ int cuhnsw_set_stream(cuhnsw_handle* h, void* cuda_stream);
 /* cudaDeviceSynchronize of the reference (cpp/src/cuhnsw_build.cu:80,185,275), on the engine's stream */
 int cuhnsw_synchronize(cuhnsw_handle* h);
 
+/* For hosts without a CUDA binding of their own (the Python layer's search_knn_batches): a stream on the handle's
+ * GPU to pass to cuhnsw_set_stream, and page-locked host memory for cuhnsw_search_knn_async.  No counterpart in
+ * the reference.  cuhnsw_stream_create stores the stream in *out_stream; cuhnsw_stream_destroy first waits for
+ * it; cuhnsw_host_alloc returns NULL when the allocation fails. */
+int cuhnsw_stream_create(cuhnsw_handle* h, void** out_stream);
+int cuhnsw_stream_synchronize(cuhnsw_handle* h, void* cuda_stream);
+int cuhnsw_stream_destroy(cuhnsw_handle* h, void* cuda_stream);
+void* cuhnsw_host_alloc(cuhnsw_handle* h, size_t bytes);
+void cuhnsw_host_free(cuhnsw_handle* h, void* ptr);
+
 /* Work counters, the counterpart of acc_visited_cnt (cpp/include/cuda_search_kernels.cuh:141-143):
  * out4 = {rows gathered for a distance, layer rows expanded, greedy sweeps, keys inserted} since the last read. */
 int cuhnsw_enable_stats(cuhnsw_handle* h, int32_t on);

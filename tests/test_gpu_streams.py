@@ -106,3 +106,28 @@ def test_a_rebuild_waits_for_searches_in_flight_and_a_destroyed_stream_does_no_h
   torch.cuda.synchronize()
   assert (out[0].cpu().numpy() == want[0]).all()
   assert int(eng.search_knn(q[:100], 10, 64)[0].max()) < 5000
+
+
+@pytest.mark.parametrize("in_flight", [1, 3])
+def test_python_batch_generator_gives_the_blocking_answers_in_order(in_flight):
+  """CuHNSW.search_knn_batches: batches of different sizes (a single 1-d query and an empty batch among them)
+  through the library's own streams and page-locked buffers; also when the consumer stops early."""
+  eng, q = _engine(20000, 6000)
+  sizes = [6000, 1, 0, 2500, 6000, 37, 5999, 12]
+  batches = [np.roll(q, 313 * i, axis=0)[:m] for i, m in enumerate(sizes)]
+  batches[1] = batches[1][0]  # one query as a vector
+  got = list(eng.search_knn_batches(iter(batches), 7, 40, in_flight=in_flight))
+  assert len(got) == len(batches)
+  for b, (ids, dist, found) in zip(batches, got):
+    want = eng.search_knn(b, 7, 40) if len(np.atleast_2d(b)) and b.size else None
+    if want is None:
+      assert ids.shape == (0, 7) and dist.shape == (0, 7) and found.shape == (0,)
+      continue
+    assert (ids == want[0]).all() and (found == want[2]).all()
+    assert_same_bits(dist, want[1])
+  gen = eng.search_knn_batches(iter(batches), 7, 40, in_flight=in_flight)
+  first = next(gen)
+  gen.close()  # streams and buffers are released with searches still in flight
+  assert (first[0] == eng.search_knn(batches[0], 7, 40)[0]).all()
+  with pytest.raises(RuntimeError):
+    list(eng.search_knn_batches([q[:, :10]], 7, 40))

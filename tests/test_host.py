@@ -105,6 +105,9 @@ def test_call_order_and_argument_checks():
         search(q, 3, 10, nns, ro, np.zeros(1, np.int32))
       with pytest.raises(RuntimeError, match="topk"):
         search(q, 0, 10, nns, np.zeros((1, 3), np.float32), np.zeros(1, np.int32))
+    # the asynchronous search takes raw addresses; without a graph it must refuse before touching them
+    with pytest.raises(RuntimeError, match="no graph"):
+      b.search_knn_async(q.ctypes.data, 1, 3, 10, nns.ctypes.data, 0, 0)
     with pytest.raises(RuntimeError, match="cannot open"):
       b.load_index(os.path.join(tmp, "nope.index"))
     short = os.path.join(tmp, "short.index")
@@ -124,6 +127,11 @@ def test_fails_loudly_without_a_gpu():
     assert b.init(write_opt(tmp, {}))
     with pytest.raises(RuntimeError, match="no CUDA device"):
       b.set_data(np.zeros((4, 8), np.float32))
+    # the helpers of the asynchronous search fail the same way instead of handing out null streams or buffers
+    with pytest.raises(RuntimeError, match="no CUDA device"):
+      b.stream_create()
+    with pytest.raises(RuntimeError, match="page-lock"):
+      b.host_array((4, 8), np.float32)
 
 
 def test_option_schema_matches_config_proto():

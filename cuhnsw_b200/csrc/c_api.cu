@@ -107,6 +107,50 @@ int cuhnsw_search_knn_async(cuhnsw_handle* h, const float* qdata, int64_t num_qu
     return e.SearchGraphAsync(qdata, num_queries, topk, ef_search, nns, distances, found_cnt);
   });
 }
+namespace {
+// A call on another replica makes that replica's GPU the thread's current device; the caller (who may be in the
+// middle of its own CUDA work) gets its device back.
+struct DeviceRestore {
+  int before = -1;
+  DeviceRestore() {
+    if (cudaGetDevice(&before) != cudaSuccess) {
+      cudaGetLastError();
+      before = -1;
+    }
+  }
+  ~DeviceRestore() {
+    if (before >= 0) cudaSetDevice(before);
+  }
+};
+}  // namespace
+int cuhnsw_replica_count(const cuhnsw_handle* h) { return h ? h->replicas.count() : 0; }
+int cuhnsw_stream_create_on(cuhnsw_handle* h, int32_t replica, void** out_stream) {
+  return guarded(h, [&](hnsw::Engine& e) {
+    int rc = hnsw::kOk;
+    hnsw::Engine* r = h->replicas.Fresh(e, replica, &rc, &h->fatal);
+    if (!r) return rc;
+    DeviceRestore restore;
+    rc = r->CreateStream(out_stream);
+    if (rc != hnsw::kOk && r != &e) h->fatal = r->last_error();
+    return rc;
+  });
+}
+int cuhnsw_search_knn_async_on(cuhnsw_handle* h, int32_t replica, void* cuda_stream, const float* qdata,
+                               int64_t num_queries, int32_t topk, int32_t ef_search, int32_t* nns, float* distances,
+                               int32_t* found_cnt) {
+  return guarded(h, [&](hnsw::Engine& e) {
+    int rc = hnsw::kOk;
+    hnsw::Engine* r = h->replicas.Fresh(e, replica, &rc, &h->fatal);
+    if (!r) return rc;
+    DeviceRestore restore;
+    void* before = r->stream();
+    r->SetStream(cuda_stream);
+    rc = r->SearchGraphAsync(qdata, num_queries, topk, ef_search, nns, distances, found_cnt);
+    r->SetStream(before);
+    if (rc != hnsw::kOk && r != &e) h->fatal = r->last_error();
+    return rc;
+  });
+}
 int cuhnsw_search_knn_noalloc(cuhnsw_handle* h, const float* qdata, int64_t num_queries, int32_t topk,
                               int32_t ef_search, int32_t* nns, float* distances, int32_t* found_cnt) {
   return guarded(h, [&](hnsw::Engine& e) {

@@ -120,6 +120,7 @@ class Engine {
   // distances between stored rows (host index arrays, host output)
   int BatchDistance(const int* src, const int* dst, long long npairs, float* out);
   int SetStream(void* stream);
+  void* stream() const { return stream_; }
   int Synchronize();
   // a stream on this engine's GPU / page-locked host memory, for hosts that have no CUDA binding of their own
   int CreateStream(void** out);

@@ -96,6 +96,19 @@ class ReplicaSet {
     return kOk;
   }
   bool active() const { return !extra_.empty(); }
+  int count() const { return 1 + (int)extra_.size(); }
+  // Replica `index` (0 = the primary) with an up-to-date copy of the index, or nullptr with *rc and *err set.
+  Engine* Fresh(Engine& primary, int index, int* rc, std::string* err) {
+    *rc = kOk;
+    if (index < 0 || index >= count()) {
+      *rc = kInvalidArgument;
+      *err = "no replica " + std::to_string(index) + ": the handle has " + std::to_string(count());
+      return nullptr;
+    }
+    if (index == 0) return &primary;
+    if (stale_ && (*rc = Sync(primary, err)) != kOk) return nullptr;
+    return extra_[(size_t)index - 1].get();
+  }
   // the primary's index changed (set_data, build_graph, load_index): replicas are copied again before the next search
   void Invalidate() { stale_ = true; }
 

@@ -35,6 +35,11 @@ SIGNATURES = {
                                               ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
   "cuhnsw_search_knn_async": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
                                              ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+  "cuhnsw_replica_count": (ctypes.c_int, [ctypes.c_void_p]),
+  "cuhnsw_stream_create_on": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p)]),
+  "cuhnsw_search_knn_async_on": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p,
+                                                ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
+                                                ctypes.c_void_p, ctypes.c_void_p]),
   "cuhnsw_search_knn_noalloc": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
                                                ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
   "cuhnsw_batch_distance": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
@@ -208,10 +213,19 @@ class CuHNSWBind:
     """What the last set_stream was given (0 / None: the default stream)."""
     return self._stream
 
-  def stream_create(self):
+  def stream_create(self, replica=0):
+    """A stream on the GPU of replica `replica` (0: the handle's own or first GPU)."""
     out = ctypes.c_void_p()
-    self._check(self._lib.cuhnsw_stream_create(self._h, ctypes.byref(out)))
+    self._check(self._lib.cuhnsw_stream_create_on(self._h, replica, ctypes.byref(out)))
     return out.value
+
+  def replica_count(self):
+    return int(self._lib.cuhnsw_replica_count(self._h))
+
+  def search_knn_async_on(self, replica, stream_ptr, q_ptr, nq, topk, ef_search, nns_ptr, dist_ptr, found_ptr):
+    """search_knn_async on one replica of a handle with `devices`, on a stream of that replica's GPU."""
+    self._check(self._lib.cuhnsw_search_knn_async_on(self._h, replica, stream_ptr, q_ptr, nq, topk, ef_search,
+                                                     nns_ptr, dist_ptr, found_ptr))
 
   def stream_synchronize(self, stream_ptr):
     self._check(self._lib.cuhnsw_stream_synchronize(self._h, stream_ptr))

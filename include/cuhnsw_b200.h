@@ -95,6 +95,16 @@ int cuhnsw_search_knn_device(cuhnsw_handle* h, const float* d_qdata, int64_t num
 int cuhnsw_search_knn_async(cuhnsw_handle* h, const float* qdata, int64_t num_queries, int32_t topk, int32_t ef_search,
                             int32_t* nns, float* distances, int32_t* found_cnt);
 
+/* The same on a handle with `devices`: replica 0 is the first listed GPU, cuhnsw_replica_count gives their number
+ * (1 without `devices`).  The stream must belong to the replica's GPU (cuhnsw_stream_create_on makes one); the
+ * handle's own stream setting is left alone.  A host that rotates its batches over the replicas, several streams
+ * each, keeps every GPU busy from one thread.  No counterpart in the reference (single device). */
+int cuhnsw_replica_count(const cuhnsw_handle* h);
+int cuhnsw_stream_create_on(cuhnsw_handle* h, int32_t replica, void** out_stream);
+int cuhnsw_search_knn_async_on(cuhnsw_handle* h, int32_t replica, void* cuda_stream, const float* qdata,
+                               int64_t num_queries, int32_t topk, int32_t ef_search, int32_t* nns, float* distances,
+                               int32_t* found_cnt);
+
 /* Search for callers that must not allocate.  No counterpart in the reference (its SearchGraph allocates a dozen
  * device vectors per call, cpp/src/cuhnsw_build.cu:241-249).  Same arguments and results as cuhnsw_search_knn (host
  * buffers), but once the index is in place (cuhnsw_set_data or cuhnsw_load_index has run on this handle: they

@@ -68,3 +68,38 @@ def test_a_device_that_does_not_exist_is_an_error_not_a_hang():
   ok.set_data(base)
   ok.build()
   assert (ok.search_knn(q, 10, 20)[2] == 10).all()
+
+
+@pytest.mark.parametrize("devices", device_lists(), ids=str)
+def test_batches_in_flight_go_round_the_replicas(devices):
+  """CuHNSW.search_knn_batches on a handle with `devices`: consecutive batches go to consecutive replicas
+  (cuhnsw_search_knn_async_on), several per replica in flight; answers equal the single-GPU answers and come
+  back in order; the caller's current device is what it was."""
+  import torch
+  base, q, opt = small_workload("angular_toy", 20000, 3000)
+  one = CuHNSW(engine_options(opt))
+  one.set_data(base)
+  one.build()
+  many = CuHNSW(engine_options(opt, devices=devices))
+  many.set_data(base)
+  many.build()
+  assert many.obj.replica_count() == len(devices) and one.obj.replica_count() == 1
+  batches = [np.roll(q, 211 * i, axis=0)[:m] for i, m in enumerate([3000, 5, 1500, 3000, 1, 2999, 64, 800, 3000])]
+  before = torch.cuda.current_device()
+  got = list(many.search_knn_batches(batches, 10, 64, in_flight=2))
+  assert torch.cuda.current_device() == before
+  assert len(got) == len(batches)
+  for b, (ids, dist, found) in zip(batches, got):
+    want = one.search_knn(b, 10, 64)
+    assert (ids == want[0]).all() and (found == want[2]).all()
+    assert_same_bits(dist, want[1])
+  # a rebuild on the primary reaches the replicas before the next batch does
+  many.set_data(base[:4000])
+  many.build()
+  one.set_data(base[:4000])
+  one.build()
+  got = list(many.search_knn_batches(batches[:4], 10, 64, in_flight=1))
+  for b, (ids, dist, found) in zip(batches[:4], got):
+    assert (ids == one.search_knn(b, 10, 64)[0]).all()
+  with pytest.raises(RuntimeError, match="no replica"):
+    many.obj.stream_create(len(devices))

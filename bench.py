@@ -782,6 +782,25 @@ def strong_block(args, engine, eopt, base, queries0, single, topk, ef, rank, wor
                 "one slice per GPU; host wall time of the blocking call (the call spans all GPUs; L2 not flushed)",
         "equals_single_gpu_answer": bool((ids_pin.numpy() == single[0]).all() and
                                          (dist_pin.numpy().view(np.uint32) == single[1].view(np.uint32)).all())}
+      # (c) the same handle, batches in flight: CuHNSW.search_knn_batches sends consecutive batches to consecutive
+      # GPUs, three per GPU in flight, from this one thread; numpy arrays in, numpy arrays out
+      try:
+        from cuhnsw_b200 import datasets as ds
+        pool = [queries0] + [ds.make_queries(args.workload, nq, 700 + s) for s in range(3)]
+        rounds = [pool[s % len(pool)] for s in range(24 * world)]
+        list(many.search_knn_batches(rounds[:4 * world], topk, ef, in_flight=3))  # streams, buffers, kernels
+        t0 = time.perf_counter()
+        got = list(many.search_knn_batches(rounds, topk, ef, in_flight=3))
+        wall = time.perf_counter() - t0
+        block["one_process_batches"] = {
+          "value": nq * len(rounds) / wall, "unit": "queries/s", "ms_per_batch": wall / len(rounds) * 1e3,
+          "batches": len(rounds), "in_flight_per_gpu": 3,
+          "what": f"CuHNSW.search_knn_batches on one handle with devices = 0..{world - 1}, one host thread; host "
+                  "wall time from the first batch handed in to the last result handed out",
+          "equals_single_gpu_answer": bool((got[0][0] == single[0]).all() and
+                                           (got[len(pool)][0] == single[0]).all())}
+      except Exception as exc:  # pylint: disable=broad-except
+        block["one_process_batches"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
       del many
     except Exception as exc:  # pylint: disable=broad-except
       block["one_call"] = {"unavailable": f"{type(exc).__name__}: {exc}"}

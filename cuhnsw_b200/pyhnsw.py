@@ -117,7 +117,7 @@ class CuHNSW:
       raise RuntimeError("search_knn_batches is already running on this index")
     obj, ef = self.obj, max(topk, ef_search)
     dims = obj.describe()["num_dims"]
-    slots = self._batch_slots  # [stream, capacity, queries, nns, distances, found, count in flight or None]
+    slots = self._batch_slots  # [stream, capacity, queries, nns, distances, found, count in flight or None, block]
     replicas = obj.replica_count()  # with the option `devices`: the batches go round the GPUs
     in_flight = max(1, in_flight) * replicas
 
@@ -129,14 +129,20 @@ class CuHNSW:
       return slot[3][:count].copy(), slot[4][:count].copy(), slot[5][:count].copy()
 
     def resize(slot, count, width):
-      for arr in slot[2:6]:
-        if arr is not None:
-          obj.host_release(arr)
+      # one page-locked block per slot (releasing such memory is slow: as few blocks as possible), cut into
+      # the four arrays at 256-byte boundaries
+      if slot[7] is not None:
+        obj.host_release(slot[7])
+      sizes = [count * width * 4, count * topk * 4, count * topk * 4, count * 4]
+      starts = [0]
+      for nbytes in sizes:
+        starts.append((starts[-1] + nbytes + 255) // 256 * 256)
+      slot[7] = block = obj.host_array((starts[-1],), np.uint8)
       slot[1] = count
-      slot[2] = obj.host_array((count, width), np.float32)
-      slot[3] = obj.host_array((count, topk), np.int32)
-      slot[4] = obj.host_array((count, topk), np.float32)
-      slot[5] = obj.host_array((count,), np.int32)
+      slot[2] = block[starts[0]:starts[0] + sizes[0]].view(np.float32).reshape(count, width)
+      slot[3] = block[starts[1]:starts[1] + sizes[1]].view(np.int32).reshape(count, topk)
+      slot[4] = block[starts[2]:starts[2] + sizes[2]].view(np.float32).reshape(count, topk)
+      slot[5] = block[starts[3]:starts[3] + sizes[3]].view(np.int32)
 
     self._batches_running = True
     try:
@@ -149,7 +155,7 @@ class CuHNSW:
         if width != dims:
           raise RuntimeError(f"queries have {width} dimensions, the index has {dims}")
         if len(slots) < in_flight:
-          slots.append([obj.stream_create(len(slots) % replicas), 0, None, None, None, None, None])
+          slots.append([obj.stream_create(len(slots) % replicas), 0, None, None, None, None, None, None])
         slot = slots[turn % min(len(slots), in_flight)]
         turn += 1
         if slot[6] is not None:

@@ -48,7 +48,7 @@ def _draw(seed):
   nq = int(rng.choice([1, 7, 150, 1200]))
   q = (rng.integers(0, 3, (nq, d)) if kind == 1 else rng.standard_normal((nq, d))).astype(np.float32)
   c["topk"] = int(rng.choice([1, 3, 10, 40]))
-  c["ef"] = int(rng.choice([1, 10, 64, 200, 700]))
+  c["ef"] = int(rng.choice([1, 10, 64, 200, 700, 3000]))  # 3000: lists whose places are searched span by span
   return c, base, q
 
 

@@ -75,6 +75,13 @@ def run_gpu_inference_large(opt, index_path, topk, ef_search, num_queries, num_d
   el0 = time.time() - start
   LOGGER.info("elapsed for %d random queries of top@%d (ef_search: %d): %.4e sec (%.0f queries/s)", num_queries,
               topk, ef_search, el0, num_queries / el0)
+  # the same queries as a stream of 10 000-query batches, several of them in flight on the GPU
+  chunks = [queries[s:s + 10000] for s in range(0, num_queries, 10000)]
+  start = time.time()
+  found = sum(int(cnt.sum()) for _, _, cnt in ch0.search_knn_batches(chunks, topk, ef_search))
+  el1 = time.time() - start
+  LOGGER.info("as %d batches in flight: %.4e sec (%.0f queries/s), %d neighbours found", len(chunks), el1,
+              num_queries / el1, found)
   return el0
 
 

@@ -900,6 +900,12 @@ def cpu_legs(args, g, base, queries, spec, ef, gpu_answer, counts, world, nr):
       break
   cpu = {"value": passes * len(queries) / el, "unit": "queries/s", "cores": threads, "kind": "port",
          "sample": f"{passes} passes over the first {len(queries)}-query batch, ef_search={ef}, {el:.1f} s"}
+  # one thread on a slice of the batch (about a second): what a scalar caller of the restatement gets
+  few = queries[:max(1, min(len(queries), int(len(queries) * 1.5 / max(el / passes * threads, 1e-9))))]
+  t0 = time.perf_counter()
+  oracle.search(g, few, topk, ef, nthreads=1, native=native)
+  cpu["one_thread"] = {"value": len(few) / (time.perf_counter() - t0), "unit": "queries/s",
+                       "sample": f"the first {len(few)} queries of that batch"}
   cpu_build = None
   if not args.no_cpu_build and len(base) <= 2_000_000:
     opt = spec["opt"]

@@ -456,6 +456,31 @@ def test_save_load_save_is_byte_identical_and_oracle_readable(tmp_path):
   assert all((x == y).all() for x, y in zip(a, b))
 
 
+@pytest.mark.parametrize("n,d,max_m,max_m0", [(1, 1, 2, 2), (3, 5, 4, 9), (700, 257, 32, 64), (2000, 50, 12, 24)])
+def test_files_of_odd_shapes_and_64_bit_labels_round_trip(n, d, max_m, max_m0, tmp_path):
+  """save_index puts the records together on the device: one row, link budgets that are not multiples of 8 or
+  fill two warps, rows wider than 128 floats; and labels beyond 32 bits, which only the host holds."""
+  rng = np.random.default_rng(n + d)
+  base = rng.standard_normal((n, d)).astype(np.float32)
+  opt = dict(dist_type="l2", max_m=max_m, max_m0=max_m0, ef_construction=max(max_m0, 40), seed=9)
+  eng = CuHNSW(engine_options(opt))
+  eng.set_data(base)
+  eng.build()
+  p1, p2, p3 = (str(tmp_path / f"{k}.index") for k in "abc")
+  eng.save_index(p1)
+  levels, rows0, rows_u = eng.obj.get_graph()
+  g = index_file.load(p1, "l2")
+  assert (g.vec == base).all() and (g.rows0 == rows0).all() and (g.levels == levels).all()
+  assert (g.rowsU == rows_u[:g.rowsU.shape[0]]).all() and (g.labels == np.arange(n)).all()
+  # the same index as the numpy writer lays it out, with labels that need all 64 bits
+  labels = np.arange(n, dtype=np.int64) * (1 << 33) + 7
+  index_file.save(p2, g, g.header["mult"], g.header["ef_construction"], labels=labels)
+  eng2 = CuHNSW(engine_options({"dist_type": "l2"}))
+  eng2.load_index(p2)
+  eng2.save_index(p3)
+  assert open(p2, "rb").read() == open(p3, "rb").read()
+
+
 def test_file_written_by_reference_round_trips(golden_dir, tmp_path):
   src = os.path.join(golden_dir, "ref_built_angular.index")
   eng = CuHNSW(engine_options({"dist_type": "dot"}))

@@ -80,7 +80,7 @@ def parse():
   ap.add_argument("--ef", type=int, default=None,
                   help="search at this ef_search whatever the recall sweep says (side measurements only)")
   ap.add_argument("--no-extra-blocks", action="store_true",
-                  help="N > 1: skip the strong-scaling and sharded blocks (weak-scaling line only)")
+                  help="skip the side blocks: strong scaling and sharded search at N > 1, batches in flight at N = 1")
   ap.add_argument("--no-cpu-build", action="store_true", help="skip the CPU build (no build_roofline, no cpu build time)")
   return ap.parse_args()
 

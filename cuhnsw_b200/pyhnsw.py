@@ -108,41 +108,24 @@ class CuHNSW:
 
   def search_knn_batches(self, batches, topk, ef_search, in_flight=4, normalize=False):
     """Generator over an iterable of query arrays: yields ``search_knn``'s triple for every batch, in order,
-    while keeping up to ``in_flight`` batches on the GPU at once (on every GPU of ``devices``, in turn), each on a
-    stream of its own through page-locked buffers (``cuhnsw_search_knn_async_on``).  A launch lasts as long as its longest walk; with the next
-    batches in flight that tail is filled, which is worth about 1.4 x on 10 000-query batches.  The streams and
-    buffers stay with the index for the next call (releasing page-locked memory is slow).  An addition: the
+    while keeping up to ``in_flight`` batches on the GPU at once (on every GPU of ``devices``, in turn), each on
+    a stream of its own through page-locked buffers (``cuhnsw_search_knn_async_on``).  A launch lasts as long as
+    its longest walk; with the next batches in flight that tail is filled, which is worth about 1.4 x on
+    10 000-query batches.  The streams and buffers stay with the index for the next call.  An addition: the
     reference searches one batch per blocking call (cuhnsw/pyhnsw.py:78-88 there)."""
     if self._batches_running:
       raise RuntimeError("search_knn_batches is already running on this index")
     obj, ef = self.obj, max(topk, ef_search)
     dims = obj.describe()["num_dims"]
-    slots = self._batch_slots  # [stream, capacity, queries, nns, distances, found, count in flight or None, block]
     replicas = obj.replica_count()  # with the option `devices`: the batches go round the GPUs
-    in_flight = max(1, in_flight) * replicas
+    slots, wanted = self._batch_slots, max(1, in_flight) * replicas
 
     def collect(slot):
-      obj.stream_synchronize(slot[0])
-      count, slot[6] = slot[6], None
+      obj.stream_synchronize(slot.stream)
+      count, slot.pending = slot.pending, None
       if count == 0:
         return np.empty((0, topk), np.int32), np.empty((0, topk), np.float32), np.empty((0,), np.int32)
-      return slot[3][:count].copy(), slot[4][:count].copy(), slot[5][:count].copy()
-
-    def resize(slot, count, width):
-      # one page-locked block per slot (releasing such memory is slow: as few blocks as possible), cut into
-      # the four arrays at 256-byte boundaries
-      if slot[7] is not None:
-        obj.host_release(slot[7])
-      sizes = [count * width * 4, count * topk * 4, count * topk * 4, count * 4]
-      starts = [0]
-      for nbytes in sizes:
-        starts.append((starts[-1] + nbytes + 255) // 256 * 256)
-      slot[7] = block = obj.host_array((starts[-1],), np.uint8)
-      slot[1] = count
-      slot[2] = block[starts[0]:starts[0] + sizes[0]].view(np.float32).reshape(count, width)
-      slot[3] = block[starts[1]:starts[1] + sizes[1]].view(np.int32).reshape(count, topk)
-      slot[4] = block[starts[2]:starts[2] + sizes[2]].view(np.float32).reshape(count, topk)
-      slot[5] = block[starts[3]:starts[3] + sizes[3]].view(np.int32)
+      return slot.nns[:count].copy(), slot.distances[:count].copy(), slot.found[:count].copy()
 
     self._batches_running = True
     try:
@@ -154,30 +137,60 @@ class CuHNSW:
         count, width = queries.shape
         if width != dims:
           raise RuntimeError(f"queries have {width} dimensions, the index has {dims}")
-        if len(slots) < in_flight:
-          slots.append([obj.stream_create(len(slots) % replicas), 0, None, None, None, None, None, None])
-        slot = slots[turn % min(len(slots), in_flight)]
+        if len(slots) < wanted:
+          replica = len(slots) % replicas
+          slots.append(_BatchSlot(obj.stream_create(replica), replica))
+        slot = slots[turn % min(len(slots), wanted)]
         turn += 1
-        if slot[6] is not None:
+        if slot.pending is not None:
           yield collect(slot)
         if count == 0:
-          slot[6] = 0
+          slot.pending = 0
           continue
-        if slot[1] < count or slot[2].shape[1] != width or slot[3].shape[1] != topk:
-          resize(slot, count, width)
-        slot[2][:count] = queries
-        obj.search_knn_async_on(slots.index(slot) % replicas, slot[0], slot[2].ctypes.data, count, topk, ef,
-                                slot[3].ctypes.data, slot[4].ctypes.data, slot[5].ctypes.data)
-        slot[6] = count
+        slot.fit(obj, count, width, topk)
+        slot.queries[:count] = queries
+        obj.search_knn_async_on(slot.replica, slot.stream, slot.queries.ctypes.data, count, topk, ef,
+                                slot.nns.ctypes.data, slot.distances.ctypes.data, slot.found.ctypes.data)
+        slot.pending = count
       # what is still in flight, oldest first
-      used = min(len(slots), in_flight)
+      used = min(len(slots), wanted)
       for k in range(used):
         slot = slots[(turn + k) % used]
-        if slot[6] is not None:
+        if slot.pending is not None:
           yield collect(slot)
     finally:
       for slot in slots:  # a consumer that stopped early leaves searches in flight
-        if slot[6] is not None:
-          obj.stream_synchronize(slot[0])
-          slot[6] = None
+        if slot.pending is not None:
+          obj.stream_synchronize(slot.stream)
+          slot.pending = None
       self._batches_running = False
+
+
+class _BatchSlot:
+  """One batch in flight of ``CuHNSW.search_knn_batches``: a stream on one replica's GPU and one page-locked block
+  cut into the query and result arrays."""
+  __slots__ = ("stream", "replica", "capacity", "block", "queries", "nns", "distances", "found", "pending")
+
+  def __init__(self, stream, replica):
+    self.stream, self.replica = stream, replica
+    self.capacity, self.block = 0, None
+    self.queries = self.nns = self.distances = self.found = None
+    self.pending = None  # number of queries of the batch in flight
+
+  def fit(self, obj, count, width, topk):
+    """Arrays for `count` queries of `width` dimensions and `topk` results each; grows, never shrinks."""
+    if self.capacity >= count and self.queries.shape[1] == width and self.nns.shape[1] == topk:
+      return
+    if self.block is not None:
+      obj.host_release(self.block)
+    count = max(count, self.capacity)
+    sizes = [count * width * 4, count * topk * 4, count * topk * 4, count * 4]
+    starts = [0]
+    for nbytes in sizes:  # 256-byte boundaries
+      starts.append((starts[-1] + nbytes + 255) // 256 * 256)
+    self.block = block = obj.host_array((starts[-1],), np.uint8)
+    self.capacity = count
+    self.queries = block[starts[0]:starts[0] + sizes[0]].view(np.float32).reshape(count, width)
+    self.nns = block[starts[1]:starts[1] + sizes[1]].view(np.int32).reshape(count, topk)
+    self.distances = block[starts[2]:starts[2] + sizes[2]].view(np.float32).reshape(count, topk)
+    self.found = block[starts[3]:starts[3] + sizes[3]].view(np.int32)
